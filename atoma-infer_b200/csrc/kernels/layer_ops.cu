@@ -280,19 +280,21 @@ extern "C" int scaled_add_rmsnorm(float* resid, const void* delta, int delta_dty
 //  * with q_norm / k_norm: the whole q part, and the whole k part, is divided by its root mean square (eps inside
 //    the root) and multiplied by a weight of the part's size, before the rotation;
 //  * the first `rot` dims of every q and k head rotate by position * inv_freq[i], dimension i with i + rot/2;
+//  * with head_norm: after the rotation every q head and every k head is divided by its own root mean square over d
+//    (eps inside the root; no weight);
 //  * with v_first: v <- (1 - lambda) v + lambda v_first (the same token's values of an earlier layer, rows of
 //    nkv * dv); with v_out: the layer's values (biases added) are left there for later layers;
 //  * q goes to q_out [T, nq, dp], k and v to the token's slot of its page, heads of dp elements (dp >= d, dv;
 //    the tail is zeros, so that kernels that use one head size for keys and values can read them).
 template <typename T, typename TP>
 __global__ void __launch_bounds__(256)
-qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, const TP* __restrict__ q_norm_g,
+qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __restrict__ bias_g, const TP* __restrict__ q_norm_g,
                    const TP* __restrict__ k_norm_g, float eps, const int* __restrict__ positions,
                    const int* __restrict__ token_entry, const int* __restrict__ meta, int group,
                    const float* __restrict__ inv_freq, int rot, const T* __restrict__ v_first,
                    const float* __restrict__ v_lambda, T* __restrict__ v_out, T* __restrict__ q_out,
                    T* __restrict__ cache, int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages,
-                   int store_kv, int vec4, int* __restrict__ status) {
+                   int store_kv, int vec4, int head_norm, int* __restrict__ status) {
     // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token
     extern __shared__ __align__(16) float vals[];
     __shared__ float red[66];
@@ -300,7 +302,8 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, con
     // token's position, its cosines and sines, its page.
     const int t = blockIdx.x;
     const bool live = t < meta[META_NUM_TOKENS];
-    const int NQ = nq * d, NK = nkv * d, NV = nkv * dv, half = rot / 2;
+    const int NQ = nq * d, NK = nkv * d, NV = nkv * dv;
+    int half = rot / 2;
     float* trig = vals + NQ + NK;
     const int pos = live ? positions[t] : 0;
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
@@ -320,7 +323,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, con
     const float lam = (v_first && v_lambda) ? *v_lambda : 0.f;
     const size_t head_block = (size_t)page_size * dp, kv_block = (size_t)nkv * head_block;
     {
-        const T* row = qkv + (size_t)t * (NQ + NK + NV);
+        const T* row = qkv + (size_t)t * qkv_stride;  // (the row may be the first part of a wider one)
         float sq = 0.f, sk = 0.f;
         if (vec4) {  // four values a thread (d, dv, dp and rot / 2 multiples of 4, buffers on 16 bytes)
             for (int i = threadIdx.x * 4; i < NQ + NK; i += blockDim.x * 4) {
@@ -349,6 +352,31 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, con
             if (k_norm) inv_k = rsqrtf(both[1] / (float)NK + eps);
         } else {
             __syncthreads();
+        }
+        if (head_norm) {
+            // a warp a head: the rotation in place, the head's sum of squares over the lanes in a fixed order, the division;
+            // what follows writes the heads out as they are
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+            for (int h = warp; h < nq + nkv; h += nwarps) {
+                float* hv = vals + h * d;
+                float ss = 0.f;
+                for (int i = lane; i < half; i += 32) {
+                    float lo, hi;
+                    rotate_pair(hv[i], hv[i + half], trig[i], trig[half + i], lo, hi);
+                    hv[i] = lo;
+                    hv[i + half] = hi;
+                    ss = fmaf(lo, lo, ss);
+                    ss = fmaf(hi, hi, ss);
+                }
+                for (int i = rot + lane; i < d; i += 32) ss = fmaf(hv[i], hv[i], ss);
+                ss = warp_sum(ss);
+                const float inv = rsqrtf(ss / (float)d + eps);
+                __syncwarp();
+                for (int i = lane; i < d; i += 32) hv[i] *= inv;
+            }
+            __syncthreads();
+            half = 0;
+            rot = 0;
         }
         const int slot = pos % page_size;
         T* kpage = cache + (size_t)page * 2 * kv_block + (size_t)slot * dp;
@@ -462,12 +490,13 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, con
 
 // param_dtype: the type of bias, q_norm and k_norm (bfloat16 weights of a checkpoint may stay as they are stored: the
 // kernel widens them, exactly, as it reads them, and a token's row then brings half as many weight bytes with it)
-extern "C" int qkv_prepare(const void* qkv, int dtype, const void* bias, const void* q_norm, const void* k_norm, int param_dtype, float eps,
+extern "C" int qkv_prepare(const void* qkv, long long qkv_stride, int dtype, const void* bias, const void* q_norm, const void* k_norm, int param_dtype, float eps,
                            const int* positions, const int* token_entry, const int* meta, int group, const float* inv_freq,
                            int rot, const void* v_first, const float* v_lambda, void* v_out, void* q_out, void* cache, int T,
-                           int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages, int store_kv, int* status,
-                           cudaStream_t stream) {
+                           int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages, int store_kv, int head_norm,
+                           int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (head_norm && (q_norm || k_norm)) return (int)cudaErrorInvalidValue;
     const size_t smem = ((size_t)(nq + nkv) * d + rot) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     // Few tokens: 256 threads a block, the shortest path through a token.  Many: 128, so that more blocks, each at another
@@ -475,7 +504,7 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const void* bias, const v
     const int threads = (nq + nkv) * d >= 1024 && T < 512 ? 256 : 128;
     const uintptr_t all = (uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)v_first |
                           (uintptr_t)v_out | (uintptr_t)q_out | (uintptr_t)cache;
-    const int vec4 = d % 4 == 0 && dv % 4 == 0 && dp % 4 == 0 && rot % 8 == 0 && (all & 15) == 0;
+    const int vec4 = d % 4 == 0 && dv % 4 == 0 && dp % 4 == 0 && rot % 8 == 0 && qkv_stride % 4 == 0 && (all & 15) == 0;
     cudaError_t e;
     static size_t configured[3] = {0, 0, 0};  // the attribute only ever grows (and is not set inside a capture again)
 #define PREP_CASE(TT, TP, which) \
@@ -486,9 +515,9 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const void* bias, const v
             configured[which] = smem; \
         } \
         return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT, TP>, T, threads, smem, stream, \
-                                      (const TT*)qkv, (const TP*)bias, (const TP*)q_norm, (const TP*)k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, \
+                                      (const TT*)qkv, qkv_stride, (const TP*)bias, (const TP*)q_norm, (const TP*)k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, \
                                       (const TT*)v_first, v_lambda, (TT*)v_out, (TT*)q_out, (TT*)cache, nq, nkv, d, dv, dp, \
-                                      page_size, num_pages, store_kv, vec4, status); \
+                                      page_size, num_pages, store_kv, vec4, head_norm, status); \
     } while (0)
     if (dtype == DT_F32 && param_dtype != DT_F32) return (int)cudaErrorInvalidValue;
     if (dtype == DT_F32) PREP_CASE(float, float, 0);

@@ -1,0 +1,445 @@
+// Recurrent mixers whose state is a matrix per head or per channel and whose decay differs from row to row:
+//  * gated linear attention: per head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, a_t = sigmoid(z_t)^(1/tau);
+//  * the selective scan of the Mamba kind: per channel c and state n, S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n,
+//    y_c = sum_n S[c, n] C_n + D_c u_c, times silu(z_c);
+//  * the norm per head with a weight shared by the heads, times silu(gate), behind the first.
+// Storage of projections is float32 or bfloat16; states, decays, step sizes, gates and norms are float32 always.  A
+// request's tokens run in order from its state slot (pass 0), or, for long portions, cut into chunks of time that run
+// side by side: pass 1 runs every chunk but the last from a zero state and leaves its end state and what its decays
+// amount to, a small kernel chains the chunks' start states in order, pass 3 runs every chunk again from its start
+// state and writes the outputs, the last chunk the slot.  Every sum runs in an order that depends on the sizes only.
+#include "common.cuh"
+
+#define REC_TT 16  // tokens staged in shared memory at a time
+
+int g_use_pdl = 1;
+extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+
+// ----------------------------------------------------------------------------- gated linear attention
+// q, k [T, heads * N], v [T, heads * P]: slices of wider rows (strides in elements); z float32 [T, heads * N], the decay's
+// logits before their bias.  state [slots][heads][N][P]; o float32 [T, heads * P].
+// One block per (head x column block, entry[, chunk]).  Thread (p, r) keeps NPT rows n = r * NPT .. of column p in
+// registers; R threads (a power of two, neighbouring lanes) share a column; rows beyond N see k = q = 0 and stay zero.
+template <typename T, int NPT, bool WRITE_O>
+__global__ void __launch_bounds__(256)
+gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k, long long k_stride,
+                const T* __restrict__ v, long long v_stride, const float* __restrict__ z, long long z_stride,
+                const float* __restrict__ z_bias, float inv_tau, float q_scale, float* __restrict__ state,
+                long long slot_stride, float* __restrict__ o, const int* __restrict__ meta,
+                const int* __restrict__ cu_tokens, const int* __restrict__ slots, int heads, int P, int N, int R, int PB,
+                int col_blocks, int pass, int chunk_len, int max_chunks, float* __restrict__ scratch,
+                float* __restrict__ decay) {
+    extern __shared__ __align__(16) float sm[];
+    const int SL = R > 1 ? NPT + 4 : NPT, NL = R * NPT, NP = R * SL;  // row n lies at (n / NPT) * SL + n % NPT
+    float* qs = sm;                     // [REC_TT][NP]
+    float* ks = qs + REC_TT * NP;       // [REC_TT][NP]
+    float* as = ks + REC_TT * NP;       // [REC_TT][NP]
+    float* vs = as + REC_TT * NP;       // [REC_TT][PB]
+    const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks, e = blockIdx.y, c = blockIdx.z;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (e >= meta[META_NUM_ENTRIES]) return;
+    const int first = cu_tokens[e], count = cu_tokens[e + 1] - first;
+    const int nchunks = pass == 0 ? 1 : (count + chunk_len - 1) / chunk_len;
+    if (c >= nchunks || (pass == 1 && c == nchunks - 1)) return;
+    const int t0 = first + (pass == 0 ? 0 : c * chunk_len), t1 = pass == 0 ? first + count : min(first + count, t0 + chunk_len);
+    const int tid = threadIdx.x, pl = tid / R, r = tid % R, p = cb * PB + pl;
+    const bool real = pl < PB && p < P;
+    const size_t HS = (size_t)N * P;
+    float* slot_state = state + (size_t)slots[e] * slot_stride + (size_t)h * HS;
+    float* chunk_state = scratch ? scratch + (((size_t)e * max_chunks + c) * heads + h) * HS : nullptr;
+    float S[NPT], prod[WRITE_O ? 1 : NPT];
+    const float* init = pass == 0 ? slot_state : (pass == 3 ? chunk_state : nullptr);
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = r * NPT + i;
+        S[i] = (init && real && n < N) ? init[(size_t)n * P + p] : 0.f;
+        if constexpr (!WRITE_O) prod[i] = 1.f;
+    }
+    for (int tb = t0; tb < t1; tb += REC_TT) {
+        const int nt = min(REC_TT, t1 - tb);
+        __syncthreads();  // the previous tile is no longer read
+        for (int idx = tid; idx < nt * NL; idx += blockDim.x) {
+            const int tt = idx / NL, n = idx % NL, at = tt * NP + (n / NPT) * SL + n % NPT;
+            const size_t t = (size_t)(tb + tt);
+            float qv = 0.f, kv = 0.f, av = 1.f;
+            if (n < N) {
+                qv = to_float(q[t * q_stride + (size_t)h * N + n]) * q_scale;
+                kv = to_float(k[t * k_stride + (size_t)h * N + n]);
+                // sigmoid(x)^(1/tau) = exp(-softplus(-x) / tau)
+                const float x = z[t * z_stride + (size_t)h * N + n] + (z_bias ? z_bias[(size_t)h * N + n] : 0.f);
+                av = expf(-softplus_f(-x) * inv_tau);
+            }
+            qs[at] = qv;
+            ks[at] = kv;
+            as[at] = av;
+        }
+        for (int idx = tid; idx < nt * PB; idx += blockDim.x) {
+            const int tt = idx / PB, pc = cb * PB + idx % PB;
+            vs[idx] = pc < P ? to_float(v[(size_t)(tb + tt) * v_stride + (size_t)h * P + pc]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float vv = pl < PB ? vs[tt * PB + pl] : 0.f;
+            const float* kt = ks + tt * NP + r * SL;
+            const float* at = as + tt * NP + r * SL;
+            const float* qt = qs + tt * NP + r * SL;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; i += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kt + i);
+                const float4 a4 = *reinterpret_cast<const float4*>(at + i);
+                S[i] = fmaf(a4.x, S[i], k4.x * vv);
+                S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * vv);
+                S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * vv);
+                S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * vv);
+                if constexpr (WRITE_O) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(qt + i);
+                    acc = fmaf(S[i], q4.x, acc);
+                    acc = fmaf(S[i + 1], q4.y, acc);
+                    acc = fmaf(S[i + 2], q4.z, acc);
+                    acc = fmaf(S[i + 3], q4.w, acc);
+                } else {
+                    prod[i] *= a4.x;
+                    prod[i + 1] *= a4.y;
+                    prod[i + 2] *= a4.z;
+                    prod[i + 3] *= a4.w;
+                }
+            }
+            if (WRITE_O) {
+                for (int s = R >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+                if (real && r == 0) o[(size_t)(tb + tt) * heads * P + (size_t)h * P + p] = acc;
+            }
+        }
+    }
+    float* fin = pass == 1 ? chunk_state + (size_t)heads * HS /* the next chunk's place */
+                           : ((pass == 0 || c == nchunks - 1) ? slot_state : nullptr);
+    if (fin && real) {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n = r * NPT + i;
+            if (n < N) fin[(size_t)n * P + p] = S[i];
+        }
+    }
+    if constexpr (!WRITE_O) if (pass == 1 && cb == 0 && pl == 0) {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n = r * NPT + i;
+            if (n < N) decay[(((size_t)e * max_chunks + c) * heads + h) * N + n] = prod[i];
+        }
+    }
+}
+
+// scratch[e, 0] = the slot's state; scratch[e, c] = decay[e, c - 1] (a factor per row) * scratch[e, c - 1] + scratch[e, c].
+__global__ void __launch_bounds__(256)
+gla_chunk_states_kernel(const float* __restrict__ state, long long slot_stride, float* __restrict__ scratch,
+                        const float* __restrict__ decay, const int* __restrict__ meta, const int* __restrict__ cu_tokens,
+                        const int* __restrict__ slots, int heads, int N, int P, int chunk_len, int max_chunks) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, e = blockIdx.y;
+    if (e >= meta[META_NUM_ENTRIES]) return;
+    const int count = cu_tokens[e + 1] - cu_tokens[e], nchunks = (count + chunk_len - 1) / chunk_len;
+    const long long HS = (long long)N * P;
+    const float* src = state + (size_t)slots[e] * slot_stride + (size_t)h * HS;
+    for (long long i = (long long)blockIdx.z * blockDim.x + threadIdx.x; i < HS; i += (long long)gridDim.z * blockDim.x) {
+        const int n = (int)(i / P);
+        float s = src[i];
+        scratch[(((size_t)e * max_chunks) * heads + h) * HS + i] = s;
+        for (int c = 1; c < nchunks; ++c) {
+            float* at = scratch + (((size_t)e * max_chunks + c) * heads + h) * HS + i;
+            s = fmaf(decay[(((size_t)e * max_chunks + c - 1) * heads + h) * N + n], s, *at);
+            *at = s;
+        }
+    }
+}
+
+// Rows a thread keeps, threads a column (or channel), columns a block: the least padding, then 16 or 32 rows a thread.
+static bool rec_geometry(int N, int P, int* NPT_out, int* R_out, int* PB_out) {
+    static const int sizes[] = {16, 32, 8, 64};  // in order of preference among equal paddings
+    long best = -1;
+    for (int k = 0; k < 4; ++k) {
+        const int npt = sizes[k];
+        int R = 1;
+        while (R * npt < N) R *= 2;
+        if (R > 32) continue;
+        const long cost = (long)R * npt;
+        if (best < 0 || cost < best) best = cost, *NPT_out = npt, *R_out = R;
+    }
+    if (best < 0) return false;
+    int pb = 256 / *R_out;  // up to 256 threads a block
+    if (pb > P) pb = P;
+    *PB_out = pb;
+    return true;
+}
+
+extern "C" size_t gla_scan_scratch_floats(int S, int heads, int N, int P, int max_chunks) {
+    return (size_t)S * max_chunks * heads * ((size_t)N * P + N);
+}
+
+extern "C" int gla_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
+                        int dtype, const float* z, long long z_stride, const float* z_bias, float tau, float q_scale,
+                        float* state, long long slot_stride, float* o, const int* meta, const int* cu_tokens, const int* slots,
+                        int S, int heads, int N, int P, int chunk_len, int max_chunks, float* scratch, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    int NPT = 0, R = 0, PB = 0;
+    if (tau <= 0.f || !rec_geometry(N, P, &NPT, &R, &PB)) return (int)cudaErrorInvalidValue;
+    const int col_blocks = (P + PB - 1) / PB, threads = ((PB * R + 31) / 32) * 32;
+    const size_t smem = (size_t)(3 * REC_TT * R * (R > 1 ? NPT + 4 : NPT) + REC_TT * PB) * sizeof(float);
+    if (smem > 96 * 1024) return (int)cudaErrorInvalidValue;
+    float* decay = scratch ? scratch + (size_t)S * max_chunks * heads * (size_t)N * P : nullptr;
+    const float inv_tau = 1.f / tau;
+#define GLA_CASE(TT, K, W, pass, chunks)                                                                                    \
+    case K: {                                                                                                              \
+        static size_t configured = 0;                                                                                      \
+        if (smem > 48 * 1024 && smem > configured) {                                                                       \
+            cudaError_t ce = cudaFuncSetAttribute(gla_scan_kernel<TT, K, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (ce != cudaSuccess) return (int)ce;                                                                         \
+            configured = smem;                                                                                             \
+        }                                                                                                                  \
+        err = (int)launch_kernel(gla_scan_kernel<TT, K, W>, dim3(heads * col_blocks, S, chunks), threads, smem, stream, (const TT*)q, q_stride, \
+                                 (const TT*)k, k_stride, (const TT*)v, v_stride, z, z_stride, z_bias, inv_tau, q_scale, state, \
+                                 slot_stride, o, meta, cu_tokens, slots, heads, P, N, R, PB, col_blocks, pass, chunk_len,     \
+                                 max_chunks, scratch, decay);                                                              \
+        break;                                                                                                             \
+    }
+#define GLA_PASS(TT, W, pass, chunks)                                                                                       \
+    switch (NPT) { GLA_CASE(TT, 8, W, pass, chunks) GLA_CASE(TT, 16, W, pass, chunks) GLA_CASE(TT, 32, W, pass, chunks) GLA_CASE(TT, 64, W, pass, chunks) }
+    int err = 0;
+    if (chunk_len <= 0 || max_chunks <= 1 || !scratch) {
+        if (dtype == DT_F32) { GLA_PASS(float, true, 0, 1) } else { GLA_PASS(__nv_bfloat16, true, 0, 1) }
+        return err;
+    }
+    if (dtype == DT_F32) { GLA_PASS(float, false, 1, max_chunks) } else { GLA_PASS(__nv_bfloat16, false, 1, max_chunks) }
+    if (err) return err;
+    const int zblocks = (int)(((long long)N * P + 1023) / 1024);
+    err = (int)launch_kernel(gla_chunk_states_kernel, dim3(heads, S, zblocks), 256, 0, stream, (const float*)state, slot_stride,
+                             scratch, (const float*)decay, meta, cu_tokens, slots, heads, N, P, chunk_len, max_chunks);
+    if (err) return err;
+    if (dtype == DT_F32) { GLA_PASS(float, true, 3, max_chunks) } else { GLA_PASS(__nv_bfloat16, true, 3, max_chunks) }
+    return err;
+#undef GLA_PASS
+#undef GLA_CASE
+}
+
+// ----------------------------------------------------------------------------- norm per head, shared weight, gate
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w * silu(g[t, h, :]); o float32 [T, heads * P], g a slice of
+// wider rows, w float32 [P].  A warp a (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ g, long long g_stride, const float* __restrict__ w,
+                      float eps, T* __restrict__ out, const int* __restrict__ meta, int heads, int P) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= meta[META_NUM_TOKENS] || h >= heads) return;
+    const float* row = o + ((size_t)t * heads + h) * P;
+    const T* gate = g + (size_t)t * g_stride + (size_t)h * P;
+    float ss = 0.f;
+    for (int i = lane; i < P; i += 32) ss = fmaf(row[i], row[i], ss);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)P + eps);
+    T* dst = out + ((size_t)t * heads + h) * P;
+    for (int i = lane; i < P; i += 32) dst[i] = from_float<T>(row[i] * inv * w[i] * silu_f(to_float(gate[i])));
+}
+
+extern "C" int head_norm_gate(const float* o, const void* g, int dtype, long long g_stride, const float* w, float eps, void* out,
+                              const int* meta, int T, int heads, int P, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const dim3 grid(T, (heads + 3) / 4);
+    if (dtype == DT_F32)
+        return (int)launch_kernel(head_norm_gate_kernel<float>, grid, 128, 0, stream, o, (const float*)g, g_stride, w, eps,
+                                  (float*)out, meta, heads, P);
+    return (int)launch_kernel(head_norm_gate_kernel<__nv_bfloat16>, grid, 128, 0, stream, o, (const __nv_bfloat16*)g, g_stride, w,
+                              eps, (__nv_bfloat16*)out, meta, heads, P);
+}
+
+// ----------------------------------------------------------------------------- selective scan
+// u [T, inner] (after convolution and activation), zg [T, inner] (the gate's input): slices of wider rows; dt_raw float32
+// [T, inner] (softplus(dt_raw + dt_bias) is taken here); B at bc, C at bc + N of a row of bc_stride elements; a_log [inner, N];
+// state [slots][inner][N]; out [T, inner] = (sum_n S[c, n] C_n + D_c u_c) * silu(zg_c).
+// One block per (channel block, entry[, chunk]).  Thread (c, r) keeps NPT states n = r * NPT .. of channel c.
+#define LOG2E_F 1.4426950408889634f
+
+template <typename T, int NPT, bool WRITE_Y>
+__global__ void __launch_bounds__(256)
+selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* __restrict__ dt_raw,
+                      const float* __restrict__ dt_bias, const T* __restrict__ bc, long long bc_stride,
+                      const T* __restrict__ zg, long long z_stride, const float* __restrict__ a_log,
+                      const float* __restrict__ d_skip, float* __restrict__ state, long long slot_stride, T* __restrict__ out,
+                      const int* __restrict__ meta, const int* __restrict__ cu_tokens, const int* __restrict__ slots,
+                      int inner, int N, int R, int CPB, int pass, int chunk_len, int max_chunks, float* __restrict__ scratch,
+                      float* __restrict__ dt_sums) {
+    extern __shared__ __align__(16) float sm[];
+    const int SL = R > 1 ? NPT + 4 : NPT, NL = R * NPT, NP = R * SL;
+    float* Bs = sm;                      // [REC_TT][NP]
+    float* Cs = Bs + REC_TT * NP;        // [REC_TT][NP]
+    float* us = Cs + REC_TT * NP;        // [REC_TT][CPB]
+    float* ds = us + REC_TT * CPB;       // [REC_TT][CPB] step sizes
+    float* zs = ds + REC_TT * CPB;       // [REC_TT][CPB]
+    const int e = blockIdx.y, ch = blockIdx.z;
+    const int tid = threadIdx.x, cl = tid / R, r = tid % R, c = blockIdx.x * CPB + cl;
+    const bool real = cl < CPB && c < inner;
+    // the weights come before the wait: no kernel writes them
+    float A2[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = r * NPT + i;
+        A2[i] = (real && n < N) ? -expf(a_log[(size_t)c * N + n]) * LOG2E_F : 0.f;
+    }
+    const float dskip = real ? d_skip[c] : 0.f;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (e >= meta[META_NUM_ENTRIES]) return;
+    const int first = cu_tokens[e], count = cu_tokens[e + 1] - first;
+    const int nchunks = pass == 0 ? 1 : (count + chunk_len - 1) / chunk_len;
+    if (ch >= nchunks || (pass == 1 && ch == nchunks - 1)) return;
+    const int t0 = first + (pass == 0 ? 0 : ch * chunk_len), t1 = pass == 0 ? first + count : min(first + count, t0 + chunk_len);
+    const size_t HS = (size_t)inner * N;
+    float* slot_state = state + (size_t)slots[e] * slot_stride;
+    float* chunk_state = scratch ? scratch + ((size_t)e * max_chunks + ch) * HS : nullptr;
+    const float* init = pass == 0 ? slot_state : (pass == 3 ? chunk_state : nullptr);
+    float S[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = r * NPT + i;
+        S[i] = (init && real && n < N) ? init[(size_t)c * N + n] : 0.f;
+    }
+    float dt_sum = 0.f;
+    for (int tb = t0; tb < t1; tb += REC_TT) {
+        const int nt = min(REC_TT, t1 - tb);
+        __syncthreads();
+        for (int idx = tid; idx < nt * NL; idx += blockDim.x) {
+            const int tt = idx / NL, n = idx % NL, at = tt * NP + (n / NPT) * SL + n % NPT;
+            const T* row = bc + (size_t)(tb + tt) * bc_stride;
+            Bs[at] = n < N ? to_float(row[n]) : 0.f;
+            Cs[at] = n < N ? to_float(row[N + n]) : 0.f;
+        }
+        for (int idx = tid; idx < nt * CPB; idx += blockDim.x) {
+            const int tt = idx / CPB, cc = blockIdx.x * CPB + idx % CPB;
+            const size_t t = (size_t)(tb + tt);
+            const bool in = cc < inner;
+            us[idx] = in ? to_float(u[t * u_stride + cc]) : 0.f;
+            ds[idx] = in ? softplus_f(dt_raw[t * inner + cc] + dt_bias[cc]) : 0.f;
+            zs[idx] = (in && WRITE_Y) ? to_float(zg[t * z_stride + cc]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float uv = cl < CPB ? us[tt * CPB + cl] : 0.f, step = cl < CPB ? ds[tt * CPB + cl] : 0.f;
+            const float dx = step * uv;
+            const float* Bt = Bs + tt * NP + r * SL;
+            const float* Ct = Cs + tt * NP + r * SL;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; i += 4) {
+                const float4 b4 = *reinterpret_cast<const float4*>(Bt + i);
+                S[i] = fmaf(exp2f(step * A2[i]), S[i], dx * b4.x);
+                S[i + 1] = fmaf(exp2f(step * A2[i + 1]), S[i + 1], dx * b4.y);
+                S[i + 2] = fmaf(exp2f(step * A2[i + 2]), S[i + 2], dx * b4.z);
+                S[i + 3] = fmaf(exp2f(step * A2[i + 3]), S[i + 3], dx * b4.w);
+                if (WRITE_Y) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(Ct + i);
+                    acc = fmaf(S[i], c4.x, acc);
+                    acc = fmaf(S[i + 1], c4.y, acc);
+                    acc = fmaf(S[i + 2], c4.z, acc);
+                    acc = fmaf(S[i + 3], c4.w, acc);
+                }
+            }
+            if (WRITE_Y) {
+                for (int s = R >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+                if (real && r == 0) {
+                    const float y = fmaf(dskip, uv, acc);
+                    out[(size_t)(tb + tt) * inner + c] = from_float<T>(y * silu_f(zs[tt * CPB + cl]));
+                }
+            }
+            dt_sum += step;
+        }
+    }
+    float* fin = pass == 1 ? chunk_state + HS : ((pass == 0 || ch == nchunks - 1) ? slot_state : nullptr);
+    if (fin && real) {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n = r * NPT + i;
+            if (n < N) fin[(size_t)c * N + n] = S[i];
+        }
+    }
+    if (pass == 1 && real && r == 0) dt_sums[((size_t)e * max_chunks + ch) * inner + c] = dt_sum;
+}
+
+// scratch[e, 0] = the slot's state; scratch[e, c] = exp(A * (sum of the steps of chunk c - 1)) * scratch[e, c - 1] + scratch[e, c].
+__global__ void __launch_bounds__(256)
+selective_chunk_states_kernel(const float* __restrict__ state, long long slot_stride, float* __restrict__ scratch,
+                              const float* __restrict__ dt_sums, const float* __restrict__ a_log, const int* __restrict__ meta,
+                              const int* __restrict__ cu_tokens, const int* __restrict__ slots, int inner, int N, int chunk_len,
+                              int max_chunks) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.y;
+    if (e >= meta[META_NUM_ENTRIES]) return;
+    const int count = cu_tokens[e + 1] - cu_tokens[e], nchunks = (count + chunk_len - 1) / chunk_len;
+    const long long HS = (long long)inner * N, i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= HS) return;
+    const int c = (int)(i / N);
+    const float a2 = -expf(a_log[i]) * LOG2E_F;
+    float s = state[(size_t)slots[e] * slot_stride + i];
+    scratch[((size_t)e * max_chunks) * HS + i] = s;
+    for (int k = 1; k < nchunks; ++k) {
+        float* at = scratch + ((size_t)e * max_chunks + k) * HS + i;
+        s = fmaf(exp2f(a2 * dt_sums[((size_t)e * max_chunks + k - 1) * inner + c]), s, *at);
+        *at = s;
+    }
+}
+
+extern "C" size_t selective_scan_scratch_floats(int S, int inner, int N, int max_chunks) {
+    return (size_t)S * max_chunks * ((size_t)inner * N + inner);
+}
+
+extern "C" int selective_scan(const void* u, long long u_stride, const float* dt_raw, const float* dt_bias, const void* bc,
+                              long long bc_stride, const void* zg, long long z_stride, int dtype, const float* a_log,
+                              const float* d_skip, float* state, long long slot_stride, void* out, const int* meta,
+                              const int* cu_tokens, const int* slots, int S, int inner, int N, int chunk_len, int max_chunks,
+                              float* scratch, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    int NPT = 0, R = 0, CPB = 0;
+    if (!rec_geometry(N, inner, &NPT, &R, &CPB)) return (int)cudaErrorInvalidValue;
+    if (CPB * R > 128) CPB = 128 / R > 0 ? 128 / R : 1;  // 128 threads a block: more blocks for few requests
+    const int blocks = (inner + CPB - 1) / CPB, threads = ((CPB * R + 31) / 32) * 32;
+    const size_t smem = (size_t)(2 * REC_TT * R * (R > 1 ? NPT + 4 : NPT) + 3 * REC_TT * CPB) * sizeof(float);
+    if (smem > 96 * 1024) return (int)cudaErrorInvalidValue;
+    float* dt_sums = scratch ? scratch + (size_t)S * max_chunks * (size_t)inner * N : nullptr;
+#define SEL_CASE(TT, K, W, pass, chunks)                                                                                    \
+    case K: {                                                                                                              \
+        static size_t configured = 0;                                                                                      \
+        if (smem > 48 * 1024 && smem > configured) {                                                                       \
+            cudaError_t ce = cudaFuncSetAttribute(selective_scan_kernel<TT, K, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (ce != cudaSuccess) return (int)ce;                                                                         \
+            configured = smem;                                                                                             \
+        }                                                                                                                  \
+        err = (int)launch_kernel(selective_scan_kernel<TT, K, W>, dim3(blocks, S, chunks), threads, smem, stream, (const TT*)u, u_stride, \
+                                 dt_raw, dt_bias, (const TT*)bc, bc_stride, (const TT*)zg, z_stride, a_log, d_skip, state,       \
+                                 slot_stride, (TT*)out, meta, cu_tokens, slots, inner, N, R, CPB, pass, chunk_len, max_chunks,   \
+                                 scratch, dt_sums);                                                                        \
+        break;                                                                                                             \
+    }
+#define SEL_PASS(TT, W, pass, chunks)                                                                                       \
+    switch (NPT) { SEL_CASE(TT, 8, W, pass, chunks) SEL_CASE(TT, 16, W, pass, chunks) SEL_CASE(TT, 32, W, pass, chunks) SEL_CASE(TT, 64, W, pass, chunks) }
+    int err = 0;
+    if (chunk_len <= 0 || max_chunks <= 1 || !scratch) {
+        if (dtype == DT_F32) { SEL_PASS(float, true, 0, 1) } else { SEL_PASS(__nv_bfloat16, true, 0, 1) }
+        return err;
+    }
+    if (dtype == DT_F32) { SEL_PASS(float, false, 1, max_chunks) } else { SEL_PASS(__nv_bfloat16, false, 1, max_chunks) }
+    if (err) return err;
+    const long long HS = (long long)inner * N;
+    err = (int)launch_kernel(selective_chunk_states_kernel, dim3((unsigned)((HS + 255) / 256), S), 256, 0, stream,
+                             (const float*)state, slot_stride, scratch, (const float*)dt_sums, a_log, meta, cu_tokens, slots,
+                             inner, N, chunk_len, max_chunks);
+    if (err) return err;
+    if (dtype == DT_F32) { SEL_PASS(float, true, 3, max_chunks) } else { SEL_PASS(__nv_bfloat16, true, 3, max_chunks) }
+    return err;
+#undef SEL_PASS
+#undef SEL_CASE
+}

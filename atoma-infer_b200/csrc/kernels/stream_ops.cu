@@ -7,14 +7,23 @@
 int g_use_pdl = 1;
 extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 
-// resid[t] <- resid[t] + mult * (a[t] + b[t]) + add_rows[t] + vec, each of a, b, add_rows, vec optional;
-// out[t] = resid[t] * rsqrt(mean(resid[t]^2) + eps) * w if `out` is given.  With `rows`: works on rows[r] of the
+// resid[t] <- resid[t] + mult * (f0 a0[t] + f1 a1[t] + ...) + add_rows[t] + vec, up to four terms, each of the terms,
+// add_rows, vec optional; out[t] = resid[t] * rsqrt(mean(resid[t]^2) + eps) * w if `out` is given, and out2 likewise with
+// w2 and eps2 (two sublayers that read the same stream through norms of their own).  With `rows`: works on rows[r] of the
 // inputs, writes out[r], leaves resid untouched.  The updated row waits in shared memory between the two passes.
+#define SUM_MAX_TERMS 4
+struct SumTerms {
+    const void* p[SUM_MAX_TERMS];
+    float f[SUM_MAX_TERMS];
+    int n;
+};
+
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256)
-sum_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ a, const TD* __restrict__ b, float mult,
-                   const float* __restrict__ add_rows, const float* __restrict__ vec, const int* __restrict__ rows,
-                   const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ meta, int H, int vec4) {
+sum_rmsnorm_kernel(float* __restrict__ resid, SumTerms terms, float mult, const float* __restrict__ add_rows,
+                   const float* __restrict__ vec, const int* __restrict__ rows, const float* __restrict__ w, float eps,
+                   TO* __restrict__ out, const float* __restrict__ w2, float eps2, TO* __restrict__ out2,
+                   const int* __restrict__ meta, int H, int vec4) {
     __shared__ float red[33];
     extern __shared__ __align__(16) float row[];
     pdl_wait();
@@ -24,21 +33,30 @@ sum_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ a, const TD
     if (r >= limit) return;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float* x = resid + src * H;
-    const TD* pa = a ? a + src * H : nullptr;
-    const TD* pb = b ? b + src * H : nullptr;
+    const TD* pt[SUM_MAX_TERMS];
+#pragma unroll
+    for (int j = 0; j < SUM_MAX_TERMS; ++j) pt[j] = j < terms.n ? (const TD*)terms.p[j] + src * H : nullptr;
     const float* pr = add_rows ? add_rows + src * H : nullptr;
     float ss = 0.f;
     if (vec4) {  // four values a thread and step, 16-byte accesses; the sum's order differs from the scalar form's, but is as fixed
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
             float v[4];
             load4(x + i, v);
-            if (pa) {
-                float s[4], t[4];
-                load4(pa + i, s);
-                if (pb) {
-                    load4(pb + i, t);
+            if (terms.n > 0) {
+                float s[4];
+                load4(pt[0] + i, s);
+                if (terms.f[0] != 1.f) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) s[k] += t[k];
+                    for (int k = 0; k < 4; ++k) s[k] *= terms.f[0];
+                }
+#pragma unroll
+                for (int j = 1; j < SUM_MAX_TERMS; ++j) {
+                    if (j < terms.n) {
+                        float t[4];
+                        load4(pt[j] + i, t);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) s[k] = fmaf(terms.f[j], t[k], s[k]);
+                    }
                 }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) v[k] = fmaf(mult, s[k], v[k]);
@@ -63,9 +81,12 @@ sum_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ a, const TD
     } else {
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
             float v = x[i];
-            if (pa) {
-                float s = to_float(pa[i]);
-                if (pb) s += to_float(pb[i]);
+            if (terms.n > 0) {
+                float s = to_float(pt[0][i]);
+                if (terms.f[0] != 1.f) s *= terms.f[0];
+#pragma unroll
+                for (int j = 1; j < SUM_MAX_TERMS; ++j)
+                    if (j < terms.n) s = fmaf(terms.f[j], to_float(pt[j][i]), s);
                 v = fmaf(mult, s, v);
             }
             if (pr) v += pr[i];
@@ -77,31 +98,50 @@ sum_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ a, const TD
     }
     if (!out) return;
     ss = block_sum(ss, red);
-    const float inv = rsqrtf(ss / (float)H + eps);
+    const float inv = rsqrtf(ss / (float)H + eps), inv2 = rsqrtf(ss / (float)H + eps2);
     TO* o = out + (size_t)r * H;
+    TO* o2 = out2 ? out2 + (size_t)r * H : nullptr;
     if (vec4) {
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
-            float v[4], wv[4];
+            float v[4], wv[4], u[4];
             load4(row + i, v);
             load4(w + i, wv);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) v[k] = v[k] * inv * wv[k];
-            store4(o + i, v);
+            for (int k = 0; k < 4; ++k) u[k] = v[k] * inv * wv[k];
+            store4(o + i, u);
+            if (o2) {
+                load4(w2 + i, wv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) u[k] = v[k] * inv2 * wv[k];
+                store4(o2 + i, u);
+            }
         }
         return;
     }
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<TO>(row[i] * inv * w[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        o[i] = from_float<TO>(row[i] * inv * w[i]);
+        if (o2) o2[i] = from_float<TO>(row[i] * inv2 * w2[i]);
+    }
 }
 
-extern "C" int sum_rmsnorm(float* resid, const void* a, const void* b, int term_dtype, float mult, const float* add_rows,
-                           const float* vec, const int* rows, const float* w, float eps, void* out, int out_dtype,
-                           const int* meta, int n, int H, cudaStream_t stream) {
+extern "C" int sum_rmsnorm_terms(float* resid, int num_terms, const void* const* term_ptrs, const float* factors, int term_dtype,
+                                 float mult, const float* add_rows, const float* vec, const int* rows, const float* w, float eps,
+                                 void* out, const float* w2, float eps2, void* out2, int out_dtype, const int* meta, int n, int H,
+                                 cudaStream_t stream) {
     if (n <= 0) return 0;
+    if (num_terms < 0 || num_terms > SUM_MAX_TERMS) return (int)cudaErrorInvalidValue;
+    SumTerms terms = {};
+    terms.n = num_terms;
+    uintptr_t all = (uintptr_t)resid | (uintptr_t)add_rows | (uintptr_t)vec | (uintptr_t)w | (uintptr_t)out | (uintptr_t)w2 | (uintptr_t)out2;
+    for (int j = 0; j < num_terms; ++j) {
+        terms.p[j] = term_ptrs[j];
+        terms.f[j] = factors ? factors[j] : 1.f;
+        all |= (uintptr_t)term_ptrs[j];
+    }
     const int threads = H >= 1024 ? 256 : 128;
     const size_t smem = (size_t)H * sizeof(float);
     // four values per access: rows start on multiples of four elements and the buffers on 16 bytes
-    const int vec4 = H % 4 == 0 && (((uintptr_t)resid | (uintptr_t)a | (uintptr_t)b | (uintptr_t)add_rows | (uintptr_t)vec |
-                                     (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    const int vec4 = H % 4 == 0 && (all & 15) == 0;
 #define SUM_CASE(TD, TO)                                                                                                  \
     do {                                                                                                                  \
         static size_t configured = 0;                                                                                     \
@@ -111,7 +151,7 @@ extern "C" int sum_rmsnorm(float* resid, const void* a, const void* b, int term_
             configured = smem;                                                                                            \
         }                                                                                                                 \
         return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, sum_rmsnorm_kernel<TD, TO>, n, threads, smem, stream, resid,  \
-                                      (const TD*)a, (const TD*)b, mult, add_rows, vec, rows, w, eps, (TO*)out, meta, H, vec4); \
+                                      terms, mult, add_rows, vec, rows, w, eps, (TO*)out, w2, eps2, (TO*)out2, meta, H, vec4); \
     } while (0)
     if (term_dtype == DT_F32 && out_dtype == DT_F32) SUM_CASE(float, float);
     else if (term_dtype == DT_BF16 && out_dtype == DT_BF16) SUM_CASE(__nv_bfloat16, __nv_bfloat16);
@@ -120,13 +160,27 @@ extern "C" int sum_rmsnorm(float* resid, const void* a, const void* b, int term_
 #undef SUM_CASE
 }
 
+extern "C" int sum_rmsnorm(float* resid, const void* a, const void* b, int term_dtype, float mult, const float* add_rows,
+                           const float* vec, const int* rows, const float* w, float eps, void* out, int out_dtype,
+                           const int* meta, int n, int H, cudaStream_t stream) {
+    const void* ptrs[2] = {a, b};
+    return sum_rmsnorm_terms(resid, a ? (b ? 2 : 1) : 0, ptrs, nullptr, term_dtype, mult, add_rows, vec, rows, w, eps, out, nullptr,
+                             0.f, nullptr, out_dtype, meta, n, H, stream);
+}
+
 // ----------------------------------------------------------------------------- elementwise activations
-// kind 0: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// kind 0: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); kind 1: the square of relu, max(z, 0)^2.
 __device__ __forceinline__ float gelu_tanh(float z) {
     // 0.5 (1 + tanh u) = 1 / (1 + exp(-2u))
     const float u = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
     return z / (1.f + expf(-2.f * u));
 }
+
+__device__ __forceinline__ float relu_squared(float z) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+}
+__device__ __forceinline__ float activate(float z, int kind) { return kind == 1 ? relu_squared(z) : gelu_tanh(z); }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -144,7 +198,7 @@ activation_kernel(const T* __restrict__ z, T* __restrict__ out, const int* __res
             float t4[4];
             load4(z + i + k, t4);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[k + j] = gelu_tanh(t4[j]);
+            for (int j = 0; j < 4; ++j) v[k + j] = activate(t4[j], kind);
         }
 #pragma unroll
         for (int k = 0; k < V; k += 4) {
@@ -153,13 +207,13 @@ activation_kernel(const T* __restrict__ z, T* __restrict__ out, const int* __res
         }
         return;
     }
-    for (size_t k = i; k < total && k < i + V; ++k) out[k] = from_float<T>(gelu_tanh(to_float(z[k])));
+    for (size_t k = i; k < total && k < i + V; ++k) out[k] = from_float<T>(activate(to_float(z[k]), kind));
 }
 
 extern "C" int activation_rows(const void* z, void* out, int dtype, const int* meta, int T, int n, int kind,
                                cudaStream_t stream) {
     if (T <= 0 || n <= 0) return 0;
-    if (kind != 0) return (int)cudaErrorInvalidValue;
+    if (kind != 0 && kind != 1) return (int)cudaErrorInvalidValue;
     const int V = dtype == DT_F32 ? 4 : 8;
     const size_t total = (size_t)T * n;
     const unsigned blocks = (unsigned)((total + 256 * V - 1) / (256 * V));

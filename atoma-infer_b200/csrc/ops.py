@@ -31,6 +31,8 @@ ATTENTION_TC_SOURCES = ["kernels/attention_tcgen05.cu"]
 DECODE_STACK_SOURCES = ["kernels/decode_stack.cu"]
 # parallel blocks, state-space mixers, latent attention, routed experts: built when a model first uses one of them
 MIXER_SOURCES = ["kernels/stream_ops.cu", "kernels/ssm.cu", "kernels/latent.cu", "kernels/moe.cu"]
+# recurrences whose decay differs from row to row (gated linear attention, the selective scan): built at first use too
+RECURRENT_SOURCES = ["kernels/recurrent.cu"]
 ATTENTION_TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prefill attention
 ATTENTION_HEAD_DIMS = tuple(range(16, 257, 16))  # every head size the kernels take; the build check builds them all, a model only its own
 
@@ -125,8 +127,9 @@ class CudaOps:
         self.lib.kernels_set_pdl(int(on))
         for lib in self._attn_libs.values():
             lib.kernels_set_pdl(1 if on else 0)
-        if getattr(self, "_mixer_lib", None) is not None:
-            self._mixer_lib.kernels_set_pdl(int(on))
+        for name in ("_mixer_lib", "_recurrent_lib"):
+            if getattr(self, name, None) is not None:
+                getattr(self, name).kernels_set_pdl(int(on))
 
     @staticmethod
     def describe_status(words) -> Optional[str]:
@@ -386,21 +389,25 @@ class CudaOps:
 
     def qkv_prepare(self, qkv, ctx, cache_layer, group: int, q_out, *, nq: int, nkv: int, d: int, dv: int, dp: int,
                     page_size: int, num_pages: int, store_kv: bool, bias=None, q_norm=None, k_norm=None, eps: float = 0.0,
-                    inv_freq=None, rot: int = 0, v_first=None, v_lambda=None, v_out=None):
+                    inv_freq=None, rot: int = 0, v_first=None, v_lambda=None, v_out=None, head_norm: bool = False):
         """Rows [q | k | v] of the fused projection become attention's inputs: biases, root-mean-square norms over
         the whole q and the whole k part (weights ``q_norm`` / ``k_norm``), rotation of the first ``rot`` dims of
-        every head, v <- (1 - lambda) v + lambda v_first; q to ``q_out`` [T, nq * dp], k and v to the pages as heads of
+        every head, with ``head_norm`` every q and k head divided by its own root mean square (``eps``) after the rotation,
+        v <- (1 - lambda) v + lambda v_first; q to ``q_out`` [T, nq * dp], k and v to the pages as heads of
         dp elements (zeros behind d and dv).  ``v_out``: the values (biases added, unmixed) for later layers.
         ``bias``, ``q_norm`` and ``k_norm`` share one type, float32 or (beside bfloat16 rows) bfloat16."""
+        if head_norm and (q_norm is not None or k_norm is not None):
+            raise KernelError("attention rows are normed over the whole projection or head by head, not both")
         params = [t for t in (bias, q_norm, k_norm) if t is not None]
         if len({t.dtype for t in params}) > 1:
             raise KernelError("biases and norm weights of the attention rows must share one type")
         pcode = _code(params[0]) if params else DT_F32
-        self._check(self.lib.qkv_prepare(_p(qkv), _code(qkv), _p(bias), _p(q_norm), _p(k_norm), pcode, ctypes.c_float(eps),
+        qp, qs = self._rows(qkv, "qkv_prepare")  # (the rows may be the first part of wider ones)
+        self._check(self.lib.qkv_prepare(qp, qs, _code(qkv), _p(bias), _p(q_norm), _p(k_norm), pcode, ctypes.c_float(eps),
                                          _p(ctx.positions), _p(ctx.token_entry), _p(ctx.meta), max(group, 0), _p(inv_freq),
                                          int(rot) if inv_freq is not None else 0, _p(v_first), _p(v_lambda), _p(v_out),
                                          _p(q_out), _p(cache_layer), ctx.T, nq, nkv, d, dv, dp, page_size, num_pages,
-                                         int(store_kv), _p(self.status), self._stream()), "qkv_prepare")
+                                         int(store_kv), int(head_norm), _p(self.status), self._stream()), "qkv_prepare")
 
     def narrow(self, x, dtype):
         """Float32 rows in the compute type (rounded once); the same tensor if it has that type already."""
@@ -532,24 +539,29 @@ class CudaOps:
             raise KernelError(f"{what}: the last axis must be contiguous, got strides {t.stride()}")
         return _p(t), ctypes.c_longlong(t.stride(0)), ctypes.c_longlong(t.stride(1))
 
-    def sum_rmsnorm(self, resid, pending, w, eps: float, out, meta, n: int, rows=None):
-        """resid += mult * (sum of pending.terms) + pending.rows + pending.vector, each optional, in float32;
-        out = rmsnorm(resid) * w if ``out`` is given.  With ``rows`` the sum and the norm are taken at those rows only and
-        resid is left as it is."""
+    def sum_rmsnorm(self, resid, pending, w, eps: float, out, meta, n: int, rows=None, second=None):
+        """resid += mult * (f0 t0 + f1 t1 + ...) + pending.rows + pending.vector, each optional, in float32 (up to four
+        terms, their weights ``pending.factors``, 1 if none); out = rmsnorm(resid) * w if ``out`` is given; ``second`` =
+        (w2, eps2, out2): the same rows normed once more with another weight.  With ``rows`` the sum and the norm are
+        taken at those rows only and resid is left as it is."""
         terms = list(pending.terms) if pending is not None else []
-        if len(terms) > 2 or len({t.dtype for t in terms}) > 1:
-            raise KernelError("a pending sum has at most two terms, of one type")
-        a, b = (terms + [None, None])[:2]
-        tcode = _code(a) if a is not None else DT_F32
-        self._check(self._mixers().sum_rmsnorm(_p(resid), _p(a), _p(b), tcode, ctypes.c_float(pending.mult if pending else 1.0),
-                                               _p(pending.rows if pending else None), _p(pending.vector if pending else None),
-                                               _p(rows), _p(w), ctypes.c_float(eps), _p(out),
-                                               _code(out) if out is not None else DT_F32, _p(meta), n, resid.shape[-1],
-                                               self._stream()), "sum_rmsnorm")
+        if len(terms) > 4 or len({t.dtype for t in terms}) > 1:
+            raise KernelError("a pending sum has at most four terms, of one type")
+        factors = list(pending.weights()) if pending is not None else []
+        tcode = _code(terms[0]) if terms else DT_F32
+        w2, eps2, out2 = second if second is not None else (None, 0.0, None)
+        ptrs = (ctypes.c_void_p * 4)(*[t.data_ptr() for t in terms])
+        facs = (ctypes.c_float * 4)(*factors)
+        self._check(self._mixers().sum_rmsnorm_terms(_p(resid), len(terms), ptrs, facs, tcode,
+                                                     ctypes.c_float(pending.mult if pending else 1.0),
+                                                     _p(pending.rows if pending else None), _p(pending.vector if pending else None),
+                                                     _p(rows), _p(w), ctypes.c_float(eps), _p(out), _p(w2), ctypes.c_float(eps2),
+                                                     _p(out2), _code(out) if out is not None else DT_F32, _p(meta), n,
+                                                     resid.shape[-1], self._stream()), "sum_rmsnorm")
 
     def activation(self, z, out, kind: str, meta):
-        """out = act(z) element by element; ``kind``: "gelu_tanh"."""
-        code = {"gelu_tanh": 0}[kind]
+        """out = act(z) element by element; ``kind``: "gelu_tanh", or "relu2" (the square of relu)."""
+        code = {"gelu_tanh": 0, "relu2": 1}[kind]
         self._check(self._mixers().activation_rows(_p(z), _p(out), _code(z), _p(meta), z.shape[0], z.shape[1], code,
                                                    self._stream()), "activation_rows")
 
@@ -652,6 +664,84 @@ class CudaOps:
                                                int(rotary_dims) if inv_freq is not None else 0, _p(q_out), _p(cache_layer),
                                                _code(q_out), ctx.T, heads, kv_rank, rot_dim, padded, page_size, num_pages,
                                                int(store), _p(self.status), self._stream()), "latent_rows")
+
+    def sigmoid_gate(self, y, gate, meta):
+        """y[t, h] *= sigmoid(gate[t, h]) in place: y and gate [T, heads, N] slices with a contiguous last axis."""
+        T, heads, N = y.shape
+        yp, yt, yh = self._heads(y, "sigmoid_gate")
+        gp, gt, gh = self._heads(gate, "sigmoid_gate")
+        self._check(self._mixers().sigmoid_gate(yp, yt, yh, gp, gt, gh, _code(y), _p(meta), T, heads, N, self._stream()),
+                    "sigmoid_gate")
+
+    # ------------------------------------------------------------------ recurrences with a decay per row
+    def _recurrent(self):
+        lib = getattr(self, "_recurrent_lib", None)
+        if lib is None:
+            lib = self._recurrent_lib = build.load_library("recurrent", RECURRENT_SOURCES, cuda=True)
+            lib.gla_scan_scratch_floats.restype = ctypes.c_size_t
+            lib.selective_scan_scratch_floats.restype = ctypes.c_size_t
+            lib.kernels_set_pdl(int(self.pdl))
+        return lib
+
+    def _scan_chunks(self, ctx):
+        """(tokens of a chunk, chunks of the longest entry) when a long portion's recurrence is cut into chunks of time
+        that run side by side; (0, 1): every entry's tokens in order."""
+        longest = ctx.max_tokens_per_entry
+        chunk = self.SCAN_CHUNK if longest >= self.SCAN_CHUNK_FROM else 0
+        while chunk and longest // chunk > 256:
+            chunk *= 2
+        return chunk, (-(-longest // chunk) if chunk else 1)
+
+    @staticmethod
+    def _slot_state(state, shape, what: str):
+        if state.dtype != torch.float32 or tuple(state.shape[1:]) != tuple(shape) or not state[0].is_contiguous():
+            raise KernelError(f"{what}: the state is float32 [slots, {', '.join(map(str, shape))}] with contiguous slots")
+        return ctypes.c_longlong(state.stride(0))
+
+    def gla_scan(self, q, k, v, z, z_bias, tau: float, q_scale: float, state, ctx, o, *, heads: int, dim: int, vdim: int):
+        """Gated linear attention of every entry's tokens: per head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_scale
+        q_t), a_t = sigmoid(z_t + z_bias)^(1 / tau).  q, k [T, heads * dim] and v [T, heads * vdim] are slices of wider rows,
+        ``z`` float32 [T, heads * dim], ``state`` float32 [slots, heads, dim, vdim] (read and updated), ``o`` float32
+        [T, heads * vdim]."""
+        lib = self._recurrent()
+        slot_stride = self._slot_state(state, (heads, dim, vdim), "gla_scan")
+        if z.dtype != torch.float32 or o.dtype != torch.float32 or not o.is_contiguous():
+            raise KernelError("gla_scan: decay logits and outputs are float32")
+        (qp, qs), (kp, ks), (vp, vs), (zp, zs) = (self._rows(t, "gla_scan") for t in (q, k, v, z))
+        chunk, chunks = self._scan_chunks(ctx)
+        scratch = (torch.empty(lib.gla_scan_scratch_floats(ctx.S, heads, dim, vdim, chunks), dtype=torch.float32, device=o.device)
+                   if chunk else None)
+        self._check(lib.gla_scan(qp, qs, kp, ks, vp, vs, _code(q), zp, zs, _p(z_bias), ctypes.c_float(tau), ctypes.c_float(q_scale),
+                                 _p(state), slot_stride, _p(o), _p(ctx.meta), _p(ctx.cu_tokens), _p(ctx.state_slots), ctx.S,
+                                 heads, dim, vdim, chunk, chunks, _p(scratch), self._stream()), "gla_scan")
+        if chunk:
+            self.launches += 2
+
+    def head_norm_gate(self, o, gate, w, eps: float, out, meta, heads: int):
+        """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * w * silu(gate[t, h]): ``o`` float32 [T, heads * P], ``gate`` a
+        slice of wider rows, ``w`` float32 [P] (the same for every head)."""
+        gp, gs = self._rows(gate, "head_norm_gate")
+        self._check(self._recurrent().head_norm_gate(_p(o), gp, _code(gate), gs, _p(w), ctypes.c_float(eps), _p(out), _p(meta),
+                                                     o.shape[0], heads, o.shape[1] // heads, self._stream()), "head_norm_gate")
+
+    def selective_scan(self, u, dt_raw, dt_bias, bc, zg, a_log, d_skip, state, ctx, out, *, inner: int, nstate: int):
+        """The selective scan of every entry's tokens: per channel c and state n, S[c, n] <- exp(dt_c A[c, n]) S[c, n] +
+        dt_c u_c B_n with dt = softplus(dt_raw + dt_bias) and A = -exp(a_log); out = (S C + d_skip u) * silu(zg).  ``u`` and
+        ``zg`` [T, inner] and ``bc`` [T, 2 * nstate] (B, then C) are slices of wider rows, ``dt_raw`` float32 [T, inner],
+        ``state`` float32 [slots, inner, nstate] (read and updated), ``out`` [T, inner] in the type of ``u``."""
+        lib = self._recurrent()
+        slot_stride = self._slot_state(state, (inner, nstate), "selective_scan")
+        if dt_raw.dtype != torch.float32 or not dt_raw.is_contiguous() or not out.is_contiguous() or out.dtype != u.dtype:
+            raise KernelError("selective_scan: step sizes are contiguous float32, the output has the inputs' type")
+        (up, us), (bp, bs), (zp, zs) = (self._rows(t, "selective_scan") for t in (u, bc, zg))
+        chunk, chunks = self._scan_chunks(ctx)
+        scratch = (torch.empty(lib.selective_scan_scratch_floats(ctx.S, inner, nstate, chunks), dtype=torch.float32, device=out.device)
+                   if chunk else None)
+        self._check(lib.selective_scan(up, us, _p(dt_raw), _p(dt_bias), bp, bs, zp, zs, _code(u), _p(a_log), _p(d_skip), _p(state),
+                                       slot_stride, _p(out), _p(ctx.meta), _p(ctx.cu_tokens), _p(ctx.state_slots), ctx.S, inner,
+                                       nstate, chunk, chunks, _p(scratch), self._stream()), "selective_scan")
+        if chunk:
+            self.launches += 2
 
     def moe_route(self, h, w_router, ids, wts, meta):
         """Per token: float32 logits w_router h, softmax over all experts, the ids.shape[1] largest scores (ties to the

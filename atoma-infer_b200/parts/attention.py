@@ -22,8 +22,12 @@ Further options, all off by default:
 ``qk_norm`` ``{"eps": e}``: the whole q projection, and the whole k projection, is divided by its root mean square
 and multiplied by a weight of its size, before the rotation;
 ``v_mix`` ``{"key": name}``: the first layer with this key leaves its values for the step, every later one caches
-(1 - lambda) v + lambda v_first with its own learned scalar lambda.
-With any of the last four the rows are prepared by one kernel (``qkv_prepare``) that writes queries, keys and values
+(1 - lambda) v + lambda v_first with its own learned scalar lambda;
+``head_norm`` ``{"eps": e}``: after the rotation every q head and every k head is divided by its own root mean square
+over the head's size (no weight);
+``gate``: the heads' outputs side by side are multiplied by sigmoid(W_g x), W_g a matrix of their size that reads the
+mixer's input like the projections (it joins their fused matrix), before the output projection.
+With any of ``v_head_dim``, ``bias``, ``qk_norm``, ``v_mix``, ``head_norm`` the rows are prepared by one kernel (``qkv_prepare``) that writes queries, keys and values
 as heads of one padded size, the next multiple of 16 above both sizes, which the tensor-core kernels read like any
 other head size; the output projection's matrix gets zero columns to match.
 """
@@ -57,11 +61,17 @@ class Attention(Mixer):
         self.bias = bool(p.get("bias", False))
         self.qk_norm = p.get("qk_norm")
         self.v_mix = p.get("v_mix")
-        self.prepared = bool(self.bias or self.qk_norm is not None or self.v_mix is not None or self.v_head_dim != self.head_dim)
+        self.head_norm = p.get("head_norm")
+        self.gate = bool(p.get("gate", False))
+        if self.head_norm is not None and self.qk_norm is not None:
+            raise ValueError("qk_norm and head_norm exclude each other")
+        self.prepared = bool(self.bias or self.qk_norm is not None or self.v_mix is not None or self.head_norm is not None
+                             or self.gate or self.v_head_dim != self.head_dim)
         self.padded_dim = -(-max(self.head_dim, self.v_head_dim) // 16) * 16 if self.prepared else self.head_dim
         self.names = {"q": ".q_proj.weight", "k": ".k_proj.weight", "v": ".v_proj.weight", "o": ".o_proj.weight",
                       "q_bias": ".q_proj.bias", "k_bias": ".k_proj.bias", "v_bias": ".v_proj.bias",
-                      "q_norm": ".q_norm.weight", "k_norm": ".k_norm.weight", "v_mix": ".v_mix", **(p.get("names") or {})}
+                      "q_norm": ".q_norm.weight", "k_norm": ".k_norm.weight", "v_mix": ".v_mix", "gate": ".g_proj.weight",
+                      **(p.get("names") or {})}
         pos = dict(p.get("position") or {"kind": "none"})
         pos.setdefault("head_dim", self.head_dim)
         self.position = part_class("position", pos["kind"])(pos, prefix)
@@ -79,7 +89,8 @@ class Attention(Mixer):
         return self.num_kv_heads * self.v_head_dim
 
     def activation_width(self):
-        return max(self.q_size + self.kv_size + self.v_size, 2 * self.num_heads * self.padded_dim)
+        gate = self.num_heads * self.v_head_dim if self.gate else 0
+        return max(self.q_size + self.kv_size + self.v_size + gate, 2 * self.num_heads * self.padded_dim)
 
     def streamed_weights(self):
         return [self.w_qkv, self.w_o]
@@ -103,13 +114,16 @@ class Attention(Mixer):
                       TensorDecl(pre + n["k_norm"], (self.kv_size,), init="ones")]
         if self.v_mix is not None:
             decls.append(TensorDecl(pre + n["v_mix"], ()))
+        if self.gate:
+            decls.append(TensorDecl(pre + n["gate"], (self.num_heads * self.v_head_dim, self.hidden)))
         return decls + self.position.declare()
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         pre, n = self.prefix, self.names
         # One matrix [q; k; v]: each output element is the same dot product as before.
-        self.w_qkv = torch.cat([tensors[pre + n["q"]], tensors[pre + n["k"]], tensors[pre + n["v"]]], dim=0).contiguous()
+        self.w_qkv = torch.cat([tensors[pre + n["q"]], tensors[pre + n["k"]], tensors[pre + n["v"]]]
+                               + ([tensors[pre + n["gate"]]] if self.gate else []), dim=0).contiguous()
         self.w_o = tensors[pre + n["o"]].contiguous()
         self.position.bind(tensors, rt)
         if not self.prepared:
@@ -140,6 +154,10 @@ class Attention(Mixer):
         ops = self.rt.ops
         H, G, dp = self.num_heads, self.num_kv_heads, self.padded_dim
         qkv = ops.linear(x, self.w_qkv, meta=ctx.meta)
+        gate = None
+        if self.gate:  # the fused projection's last columns
+            n = self.q_size + self.kv_size + self.v_size
+            qkv, gate = qkv[:, :n], qkv[:, n:].view(ctx.T, H, self.v_head_dim)
         q = torch.empty((ctx.T, H * dp), dtype=x.dtype, device=x.device)
         v_first = v_out = None
         if self.v_mix is not None:
@@ -153,12 +171,15 @@ class Attention(Mixer):
         ops.qkv_prepare(qkv, ctx, cache.pages, cache.group, q, nq=H, nkv=G, d=self.head_dim, dv=self.v_head_dim, dp=dp,
                         page_size=cache.page_size, num_pages=cache.num_pages,
                         store_kv=cache.writes and cache.pages is not None, bias=self.b_qkv, q_norm=self.w_q_norm,
-                        k_norm=self.w_k_norm, eps=float((self.qk_norm or {}).get("eps", 0.0)),
+                        k_norm=self.w_k_norm, eps=float((self.qk_norm or self.head_norm or {}).get("eps", 0.0)),
                         inv_freq=rotary[0] if rotary else None, rot=rotary[1] if rotary else 0, v_first=v_first,
-                        v_lambda=self.v_lambda if v_first is not None else None, v_out=v_out)
+                        v_lambda=self.v_lambda if v_first is not None else None, v_out=v_out,
+                        **({"head_norm": True} if self.head_norm is not None else {}))
         out = torch.empty((ctx.T, H * dp), dtype=x.dtype, device=x.device)
         ops.attention(q, H * dp, cache.pages, ctx, cache.group, out, H, G, dp, cache.page_size, cache.num_pages,
                       int(self.window or 0), self.scale, chunk=self.chunk, sink=self.sink)
+        if gate is not None:
+            ops.sigmoid_gate(out.view(ctx.T, H, dp)[:, :, :self.v_head_dim], gate, ctx.meta)
         return ops.linear(out, self.w_o, meta=ctx.meta)
 
     def forward(self, x, ctx, cache):

@@ -84,15 +84,37 @@ class StepContext:
 @dataclass
 class PendingSum:
     """An addition to the residual stream that is still to be made: mult * (sum of ``terms``) + ``rows`` + ``vector``.
-    ``terms`` are a block's sublayer outputs [T, H] in the compute dtype (at most two), ``rows`` float32 [T, H],
-    ``vector`` float32 [H] (the same for every token).  The norm that follows (``Norm.forward``) takes the sum in
-    float32, term by term in this order, in the pass in which it also norms the updated row; a block that has no
+    ``terms`` are a block's sublayer outputs [T, H] in the compute dtype (at most four), ``rows`` float32 [T, H],
+    ``vector`` float32 [H] (the same for every token).  ``factors``: one weight per term (None: all 1), for a mixer whose
+    result is a weighted sum of several outputs; the sum is then ((f0 t0 + f1 t1) + ...) in this order.  A mixer may
+    return a ``PendingSum`` of terms and factors instead of a tensor.  The norm that follows (``Norm.forward``) takes the
+    sum in float32, term by term in this order, in the pass in which it also norms the updated row; a block that has no
     norm for it calls ``apply_pending``."""
 
     terms: Sequence[torch.Tensor] = ()
     mult: float = 1.0
     rows: Optional[torch.Tensor] = None
     vector: Optional[torch.Tensor] = None
+    factors: Optional[Sequence[float]] = None
+
+    def weights(self) -> Sequence[float]:
+        return tuple(self.factors) if self.factors is not None else (1.0,) * len(self.terms)
+
+
+def join_terms(parts, mult: float = 1.0) -> "PendingSum":
+    """One pending sum of several sublayer results, each a tensor or a ``PendingSum`` of weighted terms (whose own
+    factor is folded into its terms' weights)."""
+    terms, factors = [], []
+    for p in parts:
+        if isinstance(p, PendingSum):
+            if p.rows is not None or p.vector is not None:
+                raise ValueError("a sublayer's result has terms and factors only")
+            terms += list(p.terms)
+            factors += [p.mult * f for f in p.weights()]
+        else:
+            terms.append(p)
+            factors.append(1.0)
+    return PendingSum(tuple(terms), mult, factors=None if all(f == 1.0 for f in factors) else tuple(factors))
 
 
 def apply_pending(ops, resid: torch.Tensor, delta, ctx: "StepContext") -> None:

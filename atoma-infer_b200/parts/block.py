@@ -17,7 +17,7 @@ from typing import Optional
 
 import torch
 
-from .base import Block, PendingSum, apply_pending
+from .base import Block, apply_pending, join_terms
 
 _DEFAULT_NAMES = {"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm",
                   "feed_forward": "mlp"}
@@ -173,22 +173,25 @@ register_part("block", "postnorm", PostNormBlock)
 
 
 class ParallelBlock(Block):
-    """x <- x + mult * (mixer(h) + ff(h)) with h = norm1(x): one norm, both sublayers read its output.  The sum is
-    left pending as a ``PendingSum`` (both terms, the factor), which the next norm adds into the float32 stream term
-    by term.  Parameters: ``norm``, ``mixer``, ``feed_forward`` (None: the mixer alone), ``mult``, ``names``."""
+    """x <- x + mult * (mixer(h1) + ff(h2)), both sublayers reading the same x: through one norm (h2 = h1 = norm1(x)) or,
+    with ``two_norms``, each through a norm of its own (h2 = norm2(x)), both taken in the pass that adds what the block
+    before left pending.  The sum is left pending as a ``PendingSum`` (the terms, their weights if the mixer gives a
+    weighted sum, the factor), which the next norm adds into the float32 stream term by term.  Parameters: ``norm``,
+    ``mixer``, ``feed_forward`` (None: the mixer alone), ``mult``, ``two_norms``, ``names``."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
-        names = {"norm1": "norm1", "mixer": "mix", "feed_forward": "mlp", **(params.get("names") or {})}
+        names = {"norm1": "norm1", "norm2": "norm2", "mixer": "mix", "feed_forward": "mlp", **(params.get("names") or {})}
         mk = lambda fam, spec, name: part_class(fam, spec["kind"])(spec, f"{prefix}.{name}")  # noqa: E731
         self.mult = float(params.get("mult", 1.0))
         self.norm1 = mk("norm", params["norm"], names["norm1"])
         self.mixer = mk("mixer", params["mixer"], names["mixer"])
         ff = params.get("feed_forward")
         self.feed_forward = mk("feed_forward", ff, names["feed_forward"]) if ff else None
+        self.norm2 = mk("norm", params["norm"], names["norm2"]) if ff and params.get("two_norms") else None
 
     def parts(self):
-        return [p for p in (self.norm1, self.mixer, self.feed_forward) if p is not None]
+        return [p for p in (self.norm1, self.norm2, self.mixer, self.feed_forward) if p is not None]
 
     def streamed_weights(self):
         return self.mixer.streamed_weights() + (self.feed_forward.streamed_weights() if self.feed_forward else [])
@@ -205,11 +208,14 @@ class ParallelBlock(Block):
             p.bind(tensors, rt)
 
     def forward(self, resid, delta, ctx, cache):
-        h = self.norm1.forward(resid, delta, ctx)
+        if self.norm2 is not None:
+            h, h2 = self.norm1.forward_pair(resid, delta, ctx, self.norm2)
+        else:
+            h = h2 = self.norm1.forward(resid, delta, ctx)
         a = self.mixer.forward(h, ctx, cache)
         if self.feed_forward is None:
-            return PendingSum((a,), self.mult)
-        return PendingSum((a, self.feed_forward.forward(h, ctx)), self.mult)
+            return join_terms((a,), self.mult)
+        return join_terms((a, self.feed_forward.forward(h2, ctx)), self.mult)
 
 
 register_part("block", "parallel", ParallelBlock)

@@ -98,10 +98,10 @@ class DenseActFF(FeedForward):
     """Dense feed-forward with an elementwise activation: down(act(up(x))), no biases.
 
     Parameters: ``hidden``, ``intermediate``, ``activation`` (``gelu_tanh``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715
-    z^3)))), ``names`` (suffixes of up and down; default ``.up``, ``.down``).
+    z^3))); ``relu2``: max(z, 0)^2), ``names`` (suffixes of up and down; default ``.up``, ``.down``).
     """
 
-    ACTIVATIONS = ("gelu_tanh",)
+    ACTIVATIONS = ("gelu_tanh", "relu2")
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)

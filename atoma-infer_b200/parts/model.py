@@ -22,7 +22,8 @@ from .base import LayerCache, PendingSum, Runtime, StepContext, apply_pending
 from .decode_stack import MAX_ROWS as STACK_MAX_ROWS, plan_stacks
 
 # the registrations of the built-in parts
-from . import attention, block, embedding, feed_forward, filter, head, latent_attention, moe, norm, position, ssm  # noqa: F401
+from . import (attention, block, embedding, feed_forward, filter, head, latent_attention, linear_attention, moe, norm,  # noqa: F401
+               position, selective_scan, side_by_side, ssm)
 
 
 @dataclass
@@ -198,7 +199,7 @@ class DecoderModel:
                     apply_pending(self.rt.ops, resid, delta, ctx)
                     delta = PendingSum()
                 delta = PendingSum(delta.terms, delta.mult, first if add.embedding else None,
-                                   self.stream_tables[add.table][add.row] if add.table is not None else None)
+                                   self.stream_tables[add.table][add.row] if add.table is not None else None, delta.factors)
             if stack is not None and isinstance(delta, PendingSum):
                 apply_pending(self.rt.ops, resid, delta, ctx)
                 delta = None

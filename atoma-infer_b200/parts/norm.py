@@ -46,6 +46,18 @@ class RMSNorm(Norm):
             self.rt.ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, ctx.meta, n, rows=rows)
         return out
 
+    def forward_pair(self, resid, delta, ctx, other: "RMSNorm"):
+        """Adds ``delta`` into the stream once and returns the rows normed by this norm and by ``other`` (same size):
+        two sublayers that read the same stream, each through a norm of its own."""
+        if other.size != self.size:
+            raise ValueError("two norms of one stream have one size")
+        if not isinstance(delta, PendingSum):
+            delta = PendingSum((delta,) if delta is not None else ())
+        out = torch.empty((ctx.T, self.size), dtype=self.rt.dtype, device=resid.device)
+        out2 = torch.empty_like(out)
+        self.rt.ops.sum_rmsnorm(resid, delta, self.weight, self.eps, out, ctx.meta, ctx.T, second=(other.weight, other.eps, out2))
+        return out, out2
+
     def fused(self):
         return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}
 

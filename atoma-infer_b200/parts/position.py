@@ -7,7 +7,8 @@ dtype, per layer (:189-198, :348); here the angle position * inv_freq and its co
 and sin are computed in float32 inside the kernel that also writes keys and values
 to their pages, so no table exists.  Pairs are (x[i], x[i + rot/2]) (:250).
 
-Parameters: ``head_dim``, ``theta``, ``scaling`` (dict or None), ``rotary_dim``
+Parameters: ``head_dim``, ``theta``, ``scaling`` (dict or None; ``rope_type`` ``llama3``, or ``linear``: every frequency
+divided by ``factor``), ``rotary_dim``
 (defaults to head_dim), ``exact_frequencies`` (default False: float32 arithmetic as
 above; True: theta^(-2i/rot) taken in float64 and rounded once to float32).
 ``kind: "none"`` is the same kernel with zero frequencies.
@@ -28,6 +29,8 @@ def rotary_inv_freq(head_dim: int, theta: float, scaling=None, rotary_dim=None) 
     freq = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), idx / rot)
     if not scaling or scaling.get("rope_type", "default") == "default":
         return freq
+    if scaling.get("rope_type") == "linear":  # positions stretched by a factor: every frequency divided by it
+        return (freq / torch.tensor(float(scaling["factor"]), dtype=torch.float32)).to(torch.float32)
     f32 = lambda v: torch.tensor(float(v), dtype=torch.float32)  # noqa: E731
     factor, low, high = f32(scaling["factor"]), f32(scaling["low_freq_factor"]), f32(scaling["high_freq_factor"])
     orig = f32(scaling["original_max_position_embeddings"])
@@ -50,10 +53,14 @@ class RotaryEncoding(PositionEncoding):
 
     def _frequencies(self):
         if self.params.get("exact_frequencies"):
-            if self.scaling:
-                raise ValueError("exact_frequencies goes with unscaled frequencies only")
+            kind = (self.scaling or {}).get("rope_type", "default")
+            if kind not in ("default", "linear"):
+                raise ValueError("exact_frequencies goes with unscaled or linearly scaled frequencies only")
             idx = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
-            return torch.pow(torch.tensor(self.theta, dtype=torch.float64), -idx / self.rotary_dim).to(torch.float32)
+            freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -idx / self.rotary_dim)
+            if kind == "linear":
+                freq = freq / float(self.scaling["factor"])
+            return freq.to(torch.float32)
         return rotary_inv_freq(self.head_dim, self.theta, self.scaling, self.rotary_dim)
 
     def bind(self, tensors, rt):

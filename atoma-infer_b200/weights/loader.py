@@ -41,15 +41,45 @@ class WeightError(ValueError):
 
 
 @dataclass(frozen=True)
+class FreeDim:
+    """A size that no configuration key gives: it is whatever the checkpoint's tensor has there.  Declarations that name
+    the same free size must agree (the two factors of a low-rank map, for instance); ``default`` is the size in
+    random-weights mode.  The part reads the size from the tensor it is bound to."""
+
+    name: str
+    default: int
+
+    def __repr__(self):
+        return f"<{self.name}>"
+
+
+def concrete_shape(shape) -> Tuple[int, ...]:
+    """A declared shape with every free size at its default."""
+    return tuple(d.default if isinstance(d, FreeDim) else int(d) for d in shape)
+
+
+def _fits(declared, found, sizes: Dict[str, int]) -> bool:
+    if len(declared) != len(found):
+        return False
+    for d, f in zip(declared, found):
+        if isinstance(d, FreeDim):
+            if sizes.setdefault(d.name, int(f)) != int(f):
+                return False
+        elif int(d) != int(f):
+            return False
+    return True
+
+
+@dataclass(frozen=True)
 class TensorDecl:
-    """One checkpoint tensor a part needs.
+    """One checkpoint tensor a part needs (``shape``: integers, or ``FreeDim`` where the checkpoint decides).
 
     init: 'normal' (N(0, std)), 'ones' (1 + N(0, jitter)), 'zeros', 'jitter' (N(0, jitter)),
     or 'index' (an integer table filled with arange modulo ``index_mod``).
     """
 
     name: str
-    shape: Tuple[int, ...]
+    shape: Tuple
     init: str = "normal"
     integer: bool = False
     index_mod: int = 0
@@ -97,12 +127,15 @@ def load_tensors(
         if n not in wanted and not any(fnmatch.fnmatch(n, pat) for pat in ignore)
     ]
     wrong = []
+    free_sizes: Dict[str, int] = {}
     for d in decls:
         f = where.get(d.name)
         if f is None:
             continue
-        if tuple(f.shape(d.name)) != tuple(d.shape):
-            wrong.append((d.name, f"expected shape {list(d.shape)}, found {list(f.shape(d.name))}"))
+        if not _fits(d.shape, f.shape(d.name), free_sizes):
+            wrong.append((d.name, f"expected shape {list(d.shape)}"
+                                  + (f" with {free_sizes}" if any(isinstance(x, FreeDim) for x in d.shape) else "")
+                                  + f", found {list(f.shape(d.name))}"))
         elif d.integer == f.dtype(d.name).is_floating_point:
             kind = "an integer table" if d.integer else "a floating tensor"
             wrong.append((d.name, f"expected {kind}, found dtype {f.dtype(d.name)}"))

@@ -15,7 +15,7 @@ from typing import Dict, Mapping, Optional, Sequence
 
 import torch
 
-from .loader import TensorDecl
+from .loader import TensorDecl, concrete_shape
 from .safetensors_io import write_safetensors
 
 
@@ -30,6 +30,7 @@ def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
 def random_tensor(decl: TensorDecl, seed: int, *, std: float, norm_jitter: float,
                   dtype: torch.dtype, scale: float = 1.0, device="cpu") -> torch.Tensor:
     g = _generator(seed, decl.name, device)
+    decl = TensorDecl(decl.name, concrete_shape(decl.shape), decl.init, decl.integer, decl.index_mod)
     if decl.integer or decl.init == "index":
         n = 1
         for s in decl.shape:

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import torch
 
+import plain_bumolix as PB
 import plain_dosovik as PD
 import plain_tutezen as PT
 import plain_llama as P
@@ -128,7 +129,8 @@ class HostOps:
             self.short_conv(resid, conv[0], conv[1], ctx, conv[2], add_input=True)
 
     def qkv_prepare(self, qkv, ctx, cache, group, q_out, *, nq, nkv, d, dv, dp, page_size, num_pages, store_kv, bias=None,
-                    q_norm=None, k_norm=None, eps=0.0, inv_freq=None, rot=0, v_first=None, v_lambda=None, v_out=None):
+                    q_norm=None, k_norm=None, eps=0.0, inv_freq=None, rot=0, v_first=None, v_lambda=None, v_out=None,
+                    head_norm=False):
         self._count()
         meta = ctx.meta
         n = int(meta[META_NUM_TOKENS])
@@ -146,6 +148,8 @@ class HostOps:
             pos = ctx.positions[:n]
             q[..., :rot] = P.rope(q[..., :rot], pos, inv_freq)
             k[..., :rot] = P.rope(k[..., :rot], pos, inv_freq)
+        if head_norm:
+            q, k = PB.rms_divide(q, eps), PB.rms_divide(k, eps)
         if v_out is not None:
             v_out[:n] = v.to(v_out.dtype)
         if v_first is not None:
@@ -198,7 +202,7 @@ class HostOps:
                 out[t, h * d:(h + 1) * d] = (w @ v[:, h // g]).to(out.dtype)
 
     # -- parallel blocks, state-space mixers, latent attention, routed experts
-    def sum_rmsnorm(self, resid, pending, w, eps, out, meta, n, rows=None):
+    def sum_rmsnorm(self, resid, pending, w, eps, out, meta, n, rows=None, second=None):
         self._count()
         if rows is None:
             n = int(meta[META_NUM_TOKENS])
@@ -209,8 +213,8 @@ class HostOps:
         x = resid[idx]
         if pending is not None:
             add = torch.zeros_like(x)
-            for t in pending.terms:
-                add = add + t[idx].float()
+            for t, f in zip(pending.terms, pending.weights()):
+                add = add + f * t[idx].float()
             x = x + pending.mult * add
             if pending.rows is not None:
                 x = x + pending.rows[idx]
@@ -220,6 +224,42 @@ class HostOps:
             resid[:n] = x
         if out is not None:
             out[:n] = P.rms_norm(x, w, eps).to(out.dtype)
+        if second is not None:
+            second[2][:n] = P.rms_norm(x, second[0], second[1]).to(second[2].dtype)
+
+    def sigmoid_gate(self, y, gate, meta):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        y[:n] = (y[:n].float() * torch.sigmoid(gate[:n].float())).to(y.dtype)
+
+    def gla_scan(self, q, k, v, z, z_bias, tau, q_scale, state, ctx, o, *, heads, dim, vdim):
+        self._count()
+        for _, a, b, slot in self._entries(ctx):
+            for t in range(a, b):
+                qt, kt = q[t].float().view(heads, dim) * q_scale, k[t].float().view(heads, dim)
+                vt = v[t].float().view(heads, vdim)
+                decay = (torch.sigmoid(z[t] + z_bias) ** (1.0 / tau)).view(heads, dim)
+                for h in range(heads):
+                    S = decay[h][:, None] * state[slot, h] + torch.outer(kt[h], vt[h])
+                    state[slot, h] = S
+                    o[t, h * vdim:(h + 1) * vdim] = S.T @ qt[h]
+
+    def head_norm_gate(self, o, gate, w, eps, out, meta, heads):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        y = PB.rms_divide(o[:n].view(n, heads, -1), eps) * w
+        out[:n] = (y.reshape(n, -1) * PB.silu(gate[:n].float())).to(out.dtype)
+
+    def selective_scan(self, u, dt_raw, dt_bias, bc, zg, a_log, d_skip, state, ctx, out, *, inner, nstate):
+        self._count()
+        A = -torch.exp(a_log)
+        for _, a, b, slot in self._entries(ctx):
+            for t in range(a, b):
+                ut, dt = u[t].float(), PB.softplus(dt_raw[t] + dt_bias)
+                B, C = bc[t, :nstate].float(), bc[t, nstate:].float()
+                S = torch.exp(dt[:, None] * A) * state[slot] + (dt * ut)[:, None] * B[None, :]
+                state[slot] = S
+                out[t] = ((S @ C + d_skip * ut) * PB.silu(zg[t].float())).to(out.dtype)
 
     def causal_conv_act(self, u, w, bias, state, ctx, out, *, act="silu"):
         self._count()
@@ -311,7 +351,7 @@ class HostOps:
     def activation(self, z, out, kind, meta):
         self._count()
         n = int(meta[META_NUM_TOKENS])
-        out[:n] = {"gelu_tanh": PT.gelu_tanh}[kind](z[:n].float()).to(out.dtype)
+        out[:n] = {"gelu_tanh": PT.gelu_tanh, "relu2": PB.relu_squared}[kind](z[:n].float()).to(out.dtype)
 
     def moe_route(self, h, w_router, ids, wts, meta):
         self._count()
