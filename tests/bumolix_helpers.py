@@ -75,9 +75,12 @@ CONFIGS = {
                                    linear(5, 16, 8, 1.0), 1.0, 0.7, dense(96))], mult=0.5), 8),
 }
 
-# stds that make every mechanism matter: biases of order one, decays from fast to nearly none (so that far tokens count),
-# step sizes that differ from channel to channel, convolutions far from zero
-SCALES = {".b": 30.0, "a2": 20.0, "a1": 5.0, "A_log": 30.0, "conv": 8.0, ".dt": 10.0, ".D": 1.0}
+# stds that make every mechanism matter and leave the stream near 1, so that no layer hides the others: biases of order
+# one, decays from fast to nearly none (so that far tokens count), step sizes that differ from channel to channel and
+# decay rates over three orders of magnitude, convolutions far from zero.  A key counts wherever it is part of a name, and
+# the factors of all keys that match multiply ("mix.conv" also scales the convolution's bias).
+SCALES = {".q.b": 20.0, ".k.b": 20.0, ".v.b": 20.0, "a1": 3.0, "a2": 6.0, "a2.b": 6.0, "A_log": 30.0, "mix.conv": 8.0,
+          "conv.b": 0.75, "mix.dt": 10.0, "dt.b": 2.0, "mix.x": 4.0, "mix.o": 3.0, "mix.in": 1.4}
 
 
 def make_model(path: str, name: str, seed: int = 0) -> str:

@@ -238,7 +238,7 @@ class HostOps:
             for t in range(a, b):
                 qt, kt = q[t].float().view(heads, dim) * q_scale, k[t].float().view(heads, dim)
                 vt = v[t].float().view(heads, vdim)
-                decay = (torch.sigmoid(z[t] + z_bias) ** (1.0 / tau)).view(heads, dim)
+                decay = torch.exp(torch.nn.functional.logsigmoid(z[t] + z_bias) / tau).view(heads, dim)  # no underflow below the power
                 for h in range(heads):
                     S = decay[h][:, None] * state[slot, h] + torch.outer(kt[h], vt[h])
                     state[slot, h] = S
