@@ -11,7 +11,8 @@ fraction of the measured HBM bandwidth.  Prints ONE JSON line.
 
 ``--designs`` instead of the benchmark: prefill and decode throughput of the Dosovik design beside Llama at equal
 layer sizes, and the design's own kernels beside Llama's like kernels with their fractions of the copy bandwidth.
-``--tutezen``: the same for the Tutezen design (state-space and latent-attention layers, routed experts) at Llama's width
+``--bumolix``: the same for the Bumolix design (attention beside gated linear attention, selective-scan layers), beside
+Llama and Tutezen.  ``--tutezen``: the same for the Tutezen design (state-space and latent-attention layers, routed experts) at Llama's width
 and as many layer runs.
 
 Tables for profiles/ instead of the JSON line: ``--linears [--model 1b|3b|8b]`` (the two few-row linear
@@ -266,6 +267,22 @@ def tutezen_config(size: str, layers: int, vocab: int = 32768, window: int = 102
     return cfg
 
 
+def bumolix_config(size: str, layers: int, vocab: int = 32768, chunk: int = 1024):
+    """A Bumolix configuration of the width, heads and feed-forward size of ``size``: layers whose mixer is attention
+    (chunks of ``chunk``, half of a head rotated, positions stretched by 4) beside gated linear attention (width / 256
+    heads of 128 key channels and 256 value channels) alternate with selective-scan layers (twice the width inside, 16
+    states a channel, 4 taps, step sizes through width / 16); every layer has the dense feed-forward."""
+    H, I, nq, nkv, d = DESIGN_SIZES[size]
+    left = {"heads": nq, "kv_heads": nkv, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": chunk},
+            "rot": {"dims": d // 2, "base": 500000.0, "scaling": {"factor": 4.0}}}
+    right = {"heads": H // 256, "dim": 128, "vdim": 256, "tau": 16.0}
+    mlp = {"kind": "dense", "ff": I}
+    pair = [{"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.9}, "mlp": mlp},
+            {"type": "mamba1", "mixer": {"inner": 2 * H, "state": 16, "dt_rank": H // 16, "conv": 4}, "mlp": mlp}]
+    return {"architecture": "Bumolix", "vocab": vocab, "width": H, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+            "layers": [pair[i % 2] for i in range(layers)]}
+
+
 def design_comparison(args, other: str = "dosovik") -> int:
     """Prefill (one prompt of 2,048 tokens) and decode (8 requests, 2,048 tokens cached each, captured graphs)
     through the step function for both designs at each size; then single kernels.  Timing: CUDA events, the median
@@ -296,9 +313,13 @@ def design_comparison(args, other: str = "dosovik") -> int:
     rows = []
     for size in DESIGN_SIZES:
         pairs = design_configs(size, layers)
+        names = ("llama", other)
         if other == "tutezen":  # two layers fewer: the middle two run twice, so a step runs as many layers as Llama's
             pairs = (pairs[0], tutezen_config(size, max(layers - 2, 2)))
-        for name, cfg in zip(("llama", other), pairs):
+        if other == "bumolix":  # beside Llama (equal sizes) and Tutezen (the other design with recurrent layers)
+            names = ("llama", "tutezen", other)
+            pairs = (pairs[0], tutezen_config(size, max(layers - 2, 2)), bumolix_config(size, layers))
+        for name, cfg in zip(names, pairs):
             with tempfile.TemporaryDirectory() as d:
                 with open(os.path.join(d, "config.json"), "w") as f:
                     json.dump(cfg, f)
@@ -341,7 +362,8 @@ def design_comparison(args, other: str = "dosovik") -> int:
             print(json.dumps(row), flush=True)
             del lm
             torch.cuda.empty_cache()
-    (tutezen_kernels if other == "tutezen" else design_kernels)(make_runtime("bfloat16", "cuda:0"), hbm, median_ms)
+    kernels = {"tutezen": tutezen_kernels, "bumolix": bumolix_kernels}.get(other, design_kernels)
+    kernels(make_runtime("bfloat16", "cuda:0"), hbm, median_ms)
     return 0
 
 
@@ -555,6 +577,118 @@ def tutezen_kernels(rt, hbm, median_ms) -> None:
     ops.check_status()
 
 
+def bumolix_kernels(rt, hbm, median_ms) -> None:
+    """The Bumolix layers' own kernels beside the framework's like kernels, alone, at width 2048 (the sizes of
+    ``bumolix_config("w2048-h64", ...)``): microseconds a call and the fraction of the copy bandwidth that the bytes each
+    must move give; for the recurrences, which compute in float32, the rate of their arithmetic too.  Rows of 16,384
+    tokens and of 8 tokens (a decode step: the time of a launch inside a graph)."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import kernel_utils as K
+    from atoma_infer_b200.parts.base import PendingSum
+
+    ops, dev, bf = rt.ops, rt.device, torch.bfloat16
+    H, I, taps = 2048, 8192, 4
+    nq, nkv, d = 32, 8, 64
+    gh, gN, gP = 8, 128, 256          # gated linear attention: heads, key channels, value channels
+    inner, N, dt_rank = 4096, 16, 128  # selective scan
+    th, tP, tN, tG = 64, 64, 128, 8    # Tutezen's state-space layer at this width
+    t_inner, tC = th * tP, th * tP + 2 * tG * tN
+    print(f"kernels alone (copy bandwidth {hbm:.0f} GB/s): name, rows, us, bytes moved / time / copy bandwidth, or the rate")
+    for T in (16384, 8):
+        entries = [(0, T)] if T > 64 else [(100 + i, 1) for i in range(T)]
+        S = len(entries)
+        tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 0)
+        ctx, _ = K.make_context(rt, entries, PAGE, tables)
+        rnd = lambda *shape: torch.randn(*shape, device=dev)  # noqa: E731
+        resid, w = rnd(T, H), torch.ones(H, device=dev)
+        a, b, c = (rnd(T, H).to(bf) for _ in range(3))
+        out, out2 = (torch.empty(T, H, device=dev, dtype=bf) for _ in range(2))
+        # attention rows
+        qkv = rnd(T, (nq + 2 * nkv) * d).to(bf)
+        cache = torch.zeros(num_pages, 2, nkv, PAGE, d, device=dev, dtype=bf)
+        q_out = torch.empty(T, nq * d, device=dev, dtype=bf)
+        bias, inv_freq = torch.ones((nq + 2 * nkv) * d, device=dev, dtype=bf), torch.ones(d // 4, device=dev)
+        att, gate = rnd(T, nq, d).to(bf), rnd(T, nq, d).to(bf)
+        # gated linear attention
+        g_proj = (rnd(T, 2 * gh * gN + 2 * gh * gP) * 0.5).to(bf)
+        g_z, g_bias = rnd(T, gh * gN), torch.zeros(gh * gN, device=dev)
+        g_state, g_o = torch.zeros(S, gh, gN, gP, device=dev), torch.empty(T, gh * gP, device=dev)
+        g_y, g_w = torch.empty(T, gh * gP, device=dev, dtype=bf), torch.ones(gP, device=dev)
+        # selective scan
+        s_proj = (rnd(T, 2 * inner) * 0.5).to(bf)
+        s_cw, s_cb, s_ring = rnd(taps, inner), rnd(inner), torch.zeros(S, taps - 1, inner, device=dev)
+        s_u = torch.empty(T, inner, device=dev, dtype=bf)
+        s_low, s_dt = (rnd(T, dt_rank + 2 * N) * 0.5).to(bf), rnd(T, inner)
+        s_dtb, s_alog, s_d = torch.zeros(inner, device=dev), torch.zeros(inner, N, device=dev), torch.ones(inner, device=dev)
+        s_state, s_y = torch.zeros(S, inner, N, device=dev), torch.empty(T, inner, device=dev, dtype=bf)
+        # Tutezen's state-space layer
+        t_proj = (rnd(T, 2 * t_inner + 2 * tG * tN + th) * 0.5).to(bf)
+        t_cw, t_cb, t_ring = rnd(taps, tC), rnd(tC), torch.zeros(S, taps - 1, tC, device=dev)
+        t_xbc = torch.empty(T, tC, device=dev, dtype=bf)
+        t_state, t_y, hv = torch.zeros(S, th, tN, tP, device=dev), torch.empty(T, t_inner, device=dev), torch.ones(th, device=dev)
+        t_out, t_nw = torch.empty(T, t_inner, device=dev, dtype=bf), torch.ones(t_inner, device=dev)
+        ops.causal_conv_act(t_proj[:, t_inner:t_inner + tC], t_cw, t_cb, t_ring, ctx, t_xbc)
+        # feed-forward activations
+        z_up, act = rnd(T, I).to(bf), torch.empty(T, I, device=dev, dtype=bf)
+        gu = rnd(T, 2 * I).to(bf)
+        twice = 2 if T >= 128 else 1  # (chunks of time run twice)
+        cases = [
+            ("bumolix: weighted pending sum of three + two RMSNorms",
+             lambda: ops.sum_rmsnorm(resid, PendingSum((a, b, c), 0.7, factors=(0.6, 0.9, 1.0)), w, 1e-5, out, ctx.meta, T, second=(w, 1e-5, out2)),
+             T * H * (4 + 3 * 2 + 4 + 2 * 2), None),
+            ("tutezen: pending sum of two + RMSNorm", lambda: ops.sum_rmsnorm(resid, PendingSum((a, b), 0.5), w, 1e-5, out, ctx.meta, T),
+             T * H * (4 + 2 + 2 + 4 + 2), None),
+            ("llama:   add + RMSNorm", lambda: ops.add_rmsnorm(resid, a, w, 1e-5, out, ctx.meta, T), T * H * (4 + 2 + 4 + 2), None),
+            ("bumolix: attention rows (bias, half rotation, norm per head, pages)",
+             lambda: ops.qkv_prepare(qkv, ctx, cache, 0, q_out, nq=nq, nkv=nkv, d=d, dv=d, dp=d, page_size=PAGE, num_pages=num_pages,
+                                     store_kv=True, bias=bias, eps=1e-5, inv_freq=inv_freq, rot=d // 2, head_norm=True),
+             T * (nq + 2 * nkv) * d * 2 * 2, None),
+            ("llama:   rotation + pages", lambda: ops.rope_kv_store(qkv, ctx.positions, ctx.token_entry, ctx.meta, 0, torch.ones(d // 2, device=dev),
+                                                                    cache, num_pages, T, nq, nkv, d, d, PAGE, True),
+             T * (nq + 2 * nkv) * d * 2 * 2, None),
+            ("bumolix: output gate (sigmoid, in place)", lambda: ops.sigmoid_gate(att, gate, ctx.meta), T * nq * d * 2 * 3, None),
+            ("bumolix: gated linear attention, 8 x 128 x 256 (float32 FMA)",
+             lambda: ops.gla_scan(g_proj[:, :gh * gN], g_proj[:, gh * gN:2 * gh * gN], g_proj[:, 2 * gh * gN:2 * gh * gN + gh * gP], g_z, g_bias,
+                                  16.0, gN ** -0.5, g_state, ctx, g_o, heads=gh, dim=gN, vdim=gP),
+             T * (2 * gh * gN * 2 + gh * gP * 2 + gh * gN * 4 + gh * gP * 4) + 2 * S * gh * gN * gP * 4, 6.0 * T * gh * gN * gP * twice),
+            ("tutezen: recurrence, 64 x 128 x 64 (float32 FMA)",
+             lambda: ops.ssm_scan(t_xbc, t_proj[:, t_inner + tC:], hv, hv * 0, hv, t_state, ctx, t_y, heads=th, head_dim=tP, nstate=tN, groups=tG),
+             T * (tC * 2 + t_inner * 4) + 2 * S * th * tN * tP * 4, 6.0 * T * th * tN * tP * twice),
+            ("bumolix: norm per head, shared weight, SiLU gate", lambda: ops.head_norm_gate(g_o, g_proj[:, 2 * gh * gN + gh * gP:], g_w, 1e-5, g_y, ctx.meta, gh),
+             T * gh * gP * (4 + 2 + 2), None),
+            ("tutezen: gate, norm in 8 parts", lambda: ops.gated_group_norm(t_y, t_proj[:, :t_inner], t_nw, 8, 1e-5, t_out, ctx.meta),
+             T * t_inner * (4 + 2 + 2), None),
+            ("bumolix: convolution + bias + SiLU (+ ring), 4096 channels",
+             lambda: (ops.causal_conv_act(s_proj[:, :inner], s_cw, s_cb, s_ring, ctx, s_u) or ops.causal_conv_save(s_proj[:, :inner], s_ring, ctx, taps)),
+             T * inner * (2 + 2), None),
+            ("bumolix: selective scan, 4096 x 16, + skip, SiLU gate (float32 FMA)",
+             lambda: ops.selective_scan(s_u, s_dt, s_dtb, s_low[:, dt_rank:], s_proj[:, inner:], s_alog, s_d, s_state, ctx, s_y, inner=inner, nstate=N),
+             T * (inner * (2 + 4 + 2 + 2) + 2 * N * 2) + 2 * S * inner * N * 4, 7.0 * T * inner * N * twice),
+            ("bumolix: square of relu", lambda: ops.activation(z_up, act, "relu2", ctx.meta), T * I * 2 * 2, None),
+            ("llama:   SiLU * up", lambda: ops.silu_mul(gu, act, ctx.meta, T, I), T * I * 2 * 3, None),
+        ]
+        for name, fn, nbytes, flops in cases:
+            us = _graph_us(fn, n=16 if T <= 64 else 2)
+            rate = f"  {flops / (us * 1e-6) / 1e12:7.1f} TFLOP/s" if flops else ""
+            print(f"  {name:72s} {T:5d} rows {us:9.1f} us  {nbytes / (us * 1e-6) / (hbm * 1e9):5.2f}{rate}")
+        # attention: a prompt of T tokens (or T decode tokens over 2,048 cached ones)
+        entries = [(0, T)] if T > 64 else [(2047, 1)] * T
+        tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 1)
+        ctx, _ = K.make_context(rt, entries, PAGE, tables)
+        cache = torch.randn(num_pages, 2, nkv, PAGE, d, device=dev).to(bf)
+        q, o = torch.randn(T, nq * d, device=dev).to(bf), torch.empty(T, nq * d, device=dev, dtype=bf)
+        for name, window, kw in (("llama:   attention, 32 x 64 over 8 x 64", 0, {}), ("llama:   attention, window 1024", 1024, {}),
+                                 ("bumolix: attention, chunks of 1024 + sink", 0, {"chunk": 1024, "sink": True})):
+            us = _graph_us(lambda: ops.attention(q, nq * d, cache, ctx, 0, o, nq, nkv, d, PAGE, num_pages, window, 0.125, **kw), n=4)
+            chunk = kw.get("chunk", 0)
+            keys = (min(chunk, T) / 2 if chunk else (min(window, T) if window and T > window else T / 2)) if T > 64 else min(window or chunk or 2048, 2048)
+            flops = 4.0 * T * nq * d * keys
+            print(f"  {name:72s} {T:5d} rows {us:9.1f} us         {flops / (us * 1e-6) / 1e12:7.1f} TFLOP/s")
+    ops.check_status()
+
+
 def layer_kernel_phases(eng, args, prompt, greedy, cfg) -> int:
     """Decode steps through the persistent layer kernel (csrc/kernels/decode_stack.cu), eagerly, with every block
     writing the global clock after each phase and each barrier of each layer; prints the mean, the slowest and the
@@ -665,6 +799,9 @@ def main() -> int:
     ap.add_argument("--tutezen", action="store_true",
                     help="instead of the benchmark: prefill and decode throughput of the Tutezen design beside Llama at equal "
                          "width and as many layer runs (a JSON line each), then the design's kernels alone beside like kernels")
+    ap.add_argument("--bumolix", action="store_true",
+                    help="instead of the benchmark: prefill and decode throughput of the Bumolix design beside Llama and Tutezen "
+                         "at equal width and as many layer runs (a JSON line each), then the design's kernels alone beside like kernels")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="measure only one phase (for profiling); the JSON line then lacks the other")
     args = ap.parse_args()
@@ -685,6 +822,8 @@ def main() -> int:
         return design_comparison(args)
     if args.tutezen:
         return design_comparison(args, other="tutezen")
+    if args.bumolix:
+        return design_comparison(args, other="bumolix")
     if args.model != "1b":
         return serving_workload(args.model)
 

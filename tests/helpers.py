@@ -177,11 +177,15 @@ def run_trace(model_dir: str, dtype: str, steps, out_dir: str, max_tokens: int, 
     return steps, out_dir
 
 
-def compare_trace(steps, out_dir: str, vocab: int, ref_logits: Dict[str, torch.Tensor], strip=1, bound=2 * BF16_TOL):
+def compare_trace(steps, out_dir: str, vocab: int, ref_logits: Dict[str, torch.Tensor], strip=1, bound=2 * BF16_TOL,
+                  rounding=None):
     """Largest |difference| / largest |logit| over every wanted place, the place where it is reached (for
     messages), the share of places whose top-1 equals the plain one, and that share among the places where the
     plain top-1 leads the runner-up by more than ``bound`` times the logit scale (there a reduced-precision
-    engine has no excuse).  Request ids carry a ``strip``-letter tag."""
+    engine has no excuse).  Request ids carry a ``strip``-letter tag.  ``rounding``: per request and position the
+    error that rounding alone causes in the plain implementation; where three times that exceeds BF16_TOL, the place's
+    difference is counted in units of it (times BF16_TOL), so a place that amplifies roundings is judged by its own
+    measure and every other place as before."""
     pos: Dict[str, int] = {}
     worst, where = 0.0, None
     agree = total = clear = clear_agree = 0
@@ -202,6 +206,8 @@ def compare_trace(steps, out_dir: str, vocab: int, ref_logits: Dict[str, torch.T
             for w in e["want"]:
                 exp = ref[start + w].to(torch.float32).numpy()
                 err = float(np.abs(got[r] - exp).max()) / scale
+                if rounding is not None:
+                    err *= BF16_TOL / max(BF16_TOL, 3.0 * float(rounding[key][start + w]))
                 if not np.isfinite(got[r]).all():
                     err = float("inf")
                 if err > worst:

@@ -23,6 +23,23 @@ import torch
 
 DT = torch.float64
 
+# A yardstick for reduced precision, not a second oracle: with ROUND set to a narrower type, what a matrix product reads
+# and what it writes (and what is stored between a product and the next) is rounded to that type, everything else stays
+# as it is.  The difference from the exact run says how much a position's logits amplify such roundings.
+ROUND = None
+
+
+def rnd(x):
+    return x.to(ROUND).to(x.dtype) if ROUND is not None else x
+
+
+def lin(x, w, b=None, keep=False):
+    """w x (+ b) row by row; ``keep``: the result is not rounded (it stays wide in every mode)."""
+    y = rnd(x) @ w.T
+    if b is not None:
+        y = y + b
+    return y if keep else rnd(y)
+
 
 def rms_divide(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
@@ -76,19 +93,19 @@ def left_mixer(h, W, pre, c, eps):
     T = h.shape[0]
     H, G, D, Dv = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
     pos = torch.arange(T)
-    q = (h @ W[pre + ".q"].T + W[pre + ".q.b"]).view(T, H, D)
-    k = (h @ W[pre + ".k"].T + W[pre + ".k.b"]).view(T, G, D)
-    v = (h @ W[pre + ".v"].T + W[pre + ".v.b"]).view(T, G, Dv)
+    q = lin(h, W[pre + ".q"], W[pre + ".q.b"]).view(T, H, D)
+    k = lin(h, W[pre + ".k"], W[pre + ".k.b"]).view(T, G, D)
+    v = lin(h, W[pre + ".v"], W[pre + ".v.b"]).view(T, G, Dv)
     rot = c.get("rot")
     if rot:
         factor = (rot.get("scaling") or {}).get("factor", 1.0)
         q = rotate_leading(q, pos, rot["dims"], rot["base"], factor)
         k = rotate_leading(k, pos, rot["dims"], rot["base"], factor)
-    q, k = rms_divide(q, eps), rms_divide(k, eps)
+    q, k = rnd(rms_divide(q, eps)), rnd(rms_divide(k, eps))
     chunk = (c.get("mask") or {}).get("size", 0)
     o = chunk_sink_attention(q, k, v, c["scale"], chunk).reshape(T, H * Dv)
-    o = o * torch.sigmoid(h @ W[pre + ".g"].T)
-    return o @ W[pre + ".o"].T
+    o = rnd(o) * torch.sigmoid(lin(h, W[pre + ".g"]))
+    return lin(o, W[pre + ".o"])
 
 
 def decay_recurrence(q, k, v, a):
@@ -105,14 +122,14 @@ def decay_recurrence(q, k, v, a):
 def right_mixer(h, W, pre, c, eps):
     T = h.shape[0]
     H, N, P = c["heads"], c["dim"], c["vdim"]
-    q = (h @ W[pre + ".q"].T).view(T, H, N) * N ** -0.5
-    k = (h @ W[pre + ".k"].T).view(T, H, N)
-    v = (h @ W[pre + ".v"].T).view(T, H, P)
-    z = (h @ W[pre + ".a1"].T) @ W[pre + ".a2"].T + W[pre + ".a2.b"]
+    q = lin(h, W[pre + ".q"]).view(T, H, N) * N ** -0.5
+    k = lin(h, W[pre + ".k"]).view(T, H, N)
+    v = lin(h, W[pre + ".v"]).view(T, H, P)
+    z = lin(lin(h, W[pre + ".a1"]), W[pre + ".a2"], W[pre + ".a2.b"], keep=True)
     a = (torch.sigmoid(z) ** (1.0 / c["tau"])).view(T, H, N)
     o = torch.stack([decay_recurrence(q[:, i], k[:, i], v[:, i], a[:, i]) for i in range(H)], 1)   # [T, H, P]
     o = rms_divide(o, eps) * W[pre + ".norm"]
-    return (o.reshape(T, H * P) * silu(h @ W[pre + ".g"].T)) @ W[pre + ".o"].T
+    return lin(o.reshape(T, H * P) * silu(lin(h, W[pre + ".g"])), W[pre + ".o"])
 
 
 def parallel_mixer(h, W, pre, c, eps):
@@ -139,18 +156,18 @@ def selective_scan(u, dt, A, B, C, D):
 
 def mamba1_mixer(h, W, pre, c):
     inner, N, R = c["inner"], c["state"], c["dt_rank"]
-    xz = h @ W[pre + ".in"].T
+    xz = lin(h, W[pre + ".in"])
     u, z = xz[:, :inner], xz[:, inner:]
-    u = silu(causal_conv(u, W[pre + ".conv"], W[pre + ".conv.b"]))
-    low = u @ W[pre + ".x"].T
+    u = rnd(silu(causal_conv(u, W[pre + ".conv"], W[pre + ".conv.b"])))
+    low = lin(u, W[pre + ".x"])
     d, B, C = low[:, :R], low[:, R:R + N], low[:, R + N:]
-    dt = softplus(d @ W[pre + ".dt"].T + W[pre + ".dt.b"])
+    dt = softplus(lin(d, W[pre + ".dt"], W[pre + ".dt.b"], keep=True))
     y = selective_scan(u, dt, -torch.exp(W[pre + ".A_log"]), B, C, W[pre + ".D"])
-    return (y * silu(z)) @ W[pre + ".o"].T
+    return lin(y * silu(z), W[pre + ".o"])
 
 
 def feed_forward(h, W, pre):
-    return relu_squared(h @ W[pre + ".up"].T) @ W[pre + ".down"].T
+    return lin(relu_squared(lin(h, W[pre + ".up"])), W[pre + ".down"])
 
 
 def layer(x, W, i, ly, cfg):
@@ -167,12 +184,18 @@ def layer(x, W, i, ly, cfg):
     return x + m * a
 
 
-def forward(cfg, W, tokens, dtype=DT, streams=None):
-    """Logits [T, vocab] of one whole sequence; ``streams``: a list that receives the stream after every layer."""
+def forward(cfg, W, tokens, dtype=DT, streams=None, round_to=None):
+    """Logits [T, vocab] of one whole sequence; ``streams``: a list that receives the stream after every layer;
+    ``round_to``: the yardstick run (see ``ROUND``)."""
+    global ROUND
     W = {k: v.to(dtype) if v.is_floating_point() else v for k, v in W.items()}
     x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
-    for i, ly in enumerate(cfg["layers"]):
-        x = layer(x, W, i, ly, cfg)
-        if streams is not None:
-            streams.append(x.clone())
-    return rms_norm(x, W["final.norm"], cfg["norm"]["eps"]) @ W["embed"].T
+    ROUND = round_to
+    try:
+        for i, ly in enumerate(cfg["layers"]):
+            x = layer(x, W, i, ly, cfg)
+            if streams is not None:
+                streams.append(x.clone())
+        return lin(rms_norm(x, W["final.norm"], cfg["norm"]["eps"]), W["embed"], keep=True)
+    finally:
+        ROUND = None

@@ -44,9 +44,12 @@ def test_every_cutting_matches_plain(name, dtype, models, tmp_path):
     max_tokens = sum(-(-n // 64) * 64 for n in longest)             # pages and slots are used again
     steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), max_tokens, page)
     tol = helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL
+    # bfloat16: a first token whose query and key nearly cancel in a head that is then divided by its own size amplifies
+    # every rounding; such places are judged by what rounding does to the plain implementation there
+    rounding = BH.rounding_errors(d, cfg, seqs, ref) if dtype == "bfloat16" else None
     for tag in families:
         sub = [s for s in steps if s["entries"][0]["id"].startswith(tag)]
-        worst, where, agree, clear = helpers.compare_trace(sub, out, cfg["vocab"], ref)
+        worst, where, agree, clear = helpers.compare_trace(sub, out, cfg["vocab"], ref, rounding=rounding)
         assert worst <= tol, f"family {tag!r}: error {worst:.3g} of the logit scale at (step, request, position) {where}"
         if dtype == "float32":
             assert agree == 1.0, f"family {tag!r}: greedy tokens differ from the plain implementation"
