@@ -18,12 +18,33 @@ extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 
+// Two float32 operations in one instruction (sm_100): the recurrences' arithmetic is bound by instruction issue, and a
+// pair of neighbouring rows comes out of one 16-byte load of shared memory as two such operands.  Each half is the plain
+// IEEE operation, rounded to nearest.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)),
+          "l"(reinterpret_cast<const unsigned long long&>(c)));
+    return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)));
+    return d;
+}
+
 // ----------------------------------------------------------------------------- gated linear attention
 // q, k [T, heads * N], v [T, heads * P]: slices of wider rows (strides in elements); z float32 [T, heads * N], the decay's
 // logits before their bias.  state [slots][heads][N][P]; o float32 [T, heads * P].
-// One block per (head x column block, entry[, chunk]).  Thread (p, r) keeps NPT rows n = r * NPT .. of column p in
-// registers; R threads (a power of two, neighbouring lanes) share a column; rows beyond N see k = q = 0 and stay zero.
-template <typename T, int NPT, bool WRITE_O>
+// One block per (head x column block, entry[, chunk]).  Thread (pl, r) keeps NPT rows n = r * NPT .. of CPT neighbouring
+// columns in registers (a row's k, a and q are loaded once for all of them); R threads (a power of two, neighbouring
+// lanes) share the columns; rows beyond N see k = q = 0 and stay zero.  P is a multiple of CPT.  An output is the sum of
+// the even rows' products plus the sum of the odd rows', each in ascending order, then the R threads' sums by halving.
+template <typename T, int NPT, bool WRITE_O, int CPT>
 __global__ void __launch_bounds__(256)
 gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k, long long k_stride,
                 const T* __restrict__ v, long long v_stride, const float* __restrict__ z, long long z_stride,
@@ -46,18 +67,28 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
     const int nchunks = pass == 0 ? 1 : (count + chunk_len - 1) / chunk_len;
     if (c >= nchunks || (pass == 1 && c == nchunks - 1)) return;
     const int t0 = first + (pass == 0 ? 0 : c * chunk_len), t1 = pass == 0 ? first + count : min(first + count, t0 + chunk_len);
-    const int tid = threadIdx.x, pl = tid / R, r = tid % R, p = cb * PB + pl;
-    const bool real = pl < PB && p < P;
+    const int tid = threadIdx.x, pl = tid / R, r = tid % R, p = cb * PB + pl * CPT;
+    const bool real = pl * CPT < PB && p < P;  // all CPT columns, or none
     const size_t HS = (size_t)N * P;
     float* slot_state = state + (size_t)slots[e] * slot_stride + (size_t)h * HS;
     float* chunk_state = scratch ? scratch + (((size_t)e * max_chunks + c) * heads + h) * HS : nullptr;
-    float S[NPT], prod[WRITE_O ? 1 : NPT];
+    float2 S[CPT][NPT / 2], prod[WRITE_O ? 1 : NPT / 2];
     const float* init = pass == 0 ? slot_state : (pass == 3 ? chunk_state : nullptr);
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
         const int n = r * NPT + i;
-        S[i] = (init && real && n < N) ? init[(size_t)n * P + p] : 0.f;
-        if constexpr (!WRITE_O) prod[i] = 1.f;
+        float row[CPT];
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) row[j] = 0.f;
+        if (init && real && n < N) {
+            const float* src = init + (size_t)n * P + p;
+            if constexpr (CPT == 4) { const float4 x = *reinterpret_cast<const float4*>(src); row[0] = x.x, row[1] = x.y, row[2] = x.z, row[3] = x.w; }
+            else if constexpr (CPT == 2) { const float2 x = *reinterpret_cast<const float2*>(src); row[0] = x.x, row[1] = x.y; }
+            else row[0] = src[0];
+        }
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) (i & 1 ? S[j][i / 2].y : S[j][i / 2].x) = row[j];
+        if constexpr (!WRITE_O) prod[i / 2] = make_float2(1.f, 1.f);
     }
     for (int tb = t0; tb < t1; tb += REC_TT) {
         const int nt = min(REC_TT, t1 - tb);
@@ -83,35 +114,56 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float vv = pl < PB ? vs[tt * PB + pl] : 0.f;
+            float2 vv[CPT], acc[CPT];
+            {
+                const float* vt = vs + tt * PB + (pl * CPT < PB ? pl * CPT : 0);
+                float x[CPT];
+                if constexpr (CPT == 4) { const float4 y = *reinterpret_cast<const float4*>(vt); x[0] = y.x, x[1] = y.y, x[2] = y.z, x[3] = y.w; }
+                else if constexpr (CPT == 2) { const float2 y = *reinterpret_cast<const float2*>(vt); x[0] = y.x, x[1] = y.y; }
+                else x[0] = vt[0];
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) vv[j] = make_float2(x[j], x[j]), acc[j] = make_float2(0.f, 0.f);
+            }
             const float* kt = ks + tt * NP + r * SL;
             const float* at = as + tt * NP + r * SL;
             const float* qt = qs + tt * NP + r * SL;
-            float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < NPT; i += 4) {
                 const float4 k4 = *reinterpret_cast<const float4*>(kt + i);
                 const float4 a4 = *reinterpret_cast<const float4*>(at + i);
-                S[i] = fmaf(a4.x, S[i], k4.x * vv);
-                S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * vv);
-                S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * vv);
-                S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * vv);
+                const float2 k01 = make_float2(k4.x, k4.y), k23 = make_float2(k4.z, k4.w);
+                const float2 a01 = make_float2(a4.x, a4.y), a23 = make_float2(a4.z, a4.w);
+                float2 q01 = make_float2(0.f, 0.f), q23 = q01;
                 if constexpr (WRITE_O) {
                     const float4 q4 = *reinterpret_cast<const float4*>(qt + i);
-                    acc = fmaf(S[i], q4.x, acc);
-                    acc = fmaf(S[i + 1], q4.y, acc);
-                    acc = fmaf(S[i + 2], q4.z, acc);
-                    acc = fmaf(S[i + 3], q4.w, acc);
+                    q01 = make_float2(q4.x, q4.y), q23 = make_float2(q4.z, q4.w);
                 } else {
-                    prod[i] *= a4.x;
-                    prod[i + 1] *= a4.y;
-                    prod[i + 2] *= a4.z;
-                    prod[i + 3] *= a4.w;
+                    prod[i / 2] = mul2(prod[i / 2], a01);
+                    prod[i / 2 + 1] = mul2(prod[i / 2 + 1], a23);
+                }
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    S[j][i / 2] = fma2(a01, S[j][i / 2], mul2(k01, vv[j]));
+                    S[j][i / 2 + 1] = fma2(a23, S[j][i / 2 + 1], mul2(k23, vv[j]));
+                    if constexpr (WRITE_O) {
+                        acc[j] = fma2(S[j][i / 2], q01, acc[j]);
+                        acc[j] = fma2(S[j][i / 2 + 1], q23, acc[j]);
+                    }
                 }
             }
-            if (WRITE_O) {
-                for (int s = R >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-                if (real && r == 0) o[(size_t)(tb + tt) * heads * P + (size_t)h * P + p] = acc;
+            if constexpr (WRITE_O) {
+                float sum[CPT];
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    sum[j] = acc[j].x + acc[j].y;
+                    for (int s = R >> 1; s > 0; s >>= 1) sum[j] += __shfl_xor_sync(0xffffffffu, sum[j], s);
+                }
+                if (real && r == 0) {
+                    float* dst = o + (size_t)(tb + tt) * heads * P + (size_t)h * P + p;
+                    if constexpr (CPT == 4) *reinterpret_cast<float4*>(dst) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+                    else if constexpr (CPT == 2) *reinterpret_cast<float2*>(dst) = make_float2(sum[0], sum[1]);
+                    else dst[0] = sum[0];
+                }
             }
         }
     }
@@ -121,14 +173,22 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
             const int n = r * NPT + i;
-            if (n < N) fin[(size_t)n * P + p] = S[i];
+            if (n < N) {
+                float row[CPT];
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) row[j] = i & 1 ? S[j][i / 2].y : S[j][i / 2].x;
+                float* dst = fin + (size_t)n * P + p;
+                if constexpr (CPT == 4) *reinterpret_cast<float4*>(dst) = make_float4(row[0], row[1], row[2], row[3]);
+                else if constexpr (CPT == 2) *reinterpret_cast<float2*>(dst) = make_float2(row[0], row[1]);
+                else dst[0] = row[0];
+            }
         }
     }
     if constexpr (!WRITE_O) if (pass == 1 && cb == 0 && pl == 0) {
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
             const int n = r * NPT + i;
-            if (n < N) decay[(((size_t)e * max_chunks + c) * heads + h) * N + n] = prod[i];
+            if (n < N) decay[(((size_t)e * max_chunks + c) * heads + h) * N + n] = i & 1 ? prod[i / 2].y : prod[i / 2].x;
         }
     }
 }
@@ -157,8 +217,9 @@ gla_chunk_states_kernel(const float* __restrict__ state, long long slot_stride, 
     }
 }
 
-// Rows a thread keeps, threads a column (or channel), columns a block: the least padding, then 16 or 32 rows a thread.
-static bool rec_geometry(int N, int P, int* NPT_out, int* R_out, int* PB_out) {
+// Rows a thread keeps and threads a column (or channel): the least padding, then 16 or 32 rows a thread.  Columns a
+// block: those of up to 256 threads, ``cpt`` neighbouring columns each.
+static bool rec_geometry(int N, int P, int* NPT_out, int* R_out, int* PB_out, int cpt = 1) {
     static const int sizes[] = {16, 32, 8, 64};  // in order of preference among equal paddings
     long best = -1;
     for (int k = 0; k < 4; ++k) {
@@ -170,7 +231,7 @@ static bool rec_geometry(int N, int P, int* NPT_out, int* R_out, int* PB_out) {
         if (best < 0 || cost < best) best = cost, *NPT_out = npt, *R_out = R;
     }
     if (best < 0) return false;
-    int pb = 256 / *R_out;  // up to 256 threads a block
+    int pb = 256 / *R_out * cpt;  // up to 256 threads a block
     if (pb > P) pb = P;
     *PB_out = pb;
     return true;
@@ -187,29 +248,42 @@ extern "C" int gla_scan(const void* q, long long q_stride, const void* k, long l
     if (S <= 0) return 0;
     int NPT = 0, R = 0, PB = 0;
     if (tau <= 0.f || !rec_geometry(N, P, &NPT, &R, &PB)) return (int)cudaErrorInvalidValue;
-    const int col_blocks = (P + PB - 1) / PB, threads = ((PB * R + 31) / 32) * 32;
+    const bool chunked = chunk_len > 0 && max_chunks > 1 && scratch;
+    // Columns a thread: with chunks of time there are blocks enough, and a row's k, a and q serve four (or two) columns;
+    // a step of few tokens per entry keeps one, for as many blocks as can be.  Vector accesses want their alignment.
+    auto aligned = [&](int n) {
+        return P % n == 0 && slot_stride % n == 0 && ((uintptr_t)state | (uintptr_t)o | (uintptr_t)scratch) % (4 * n) == 0;
+    };
+    const int CPT = !chunked ? 1 : (NPT <= 16 && aligned(4) ? 4 : (NPT <= 32 && aligned(2) ? 2 : 1));
+    rec_geometry(N, P, &NPT, &R, &PB, CPT);
+    const int col_blocks = (P + PB - 1) / PB, threads = ((PB / CPT * R + 31) / 32) * 32;
     const size_t smem = (size_t)(3 * REC_TT * R * (R > 1 ? NPT + 4 : NPT) + REC_TT * PB) * sizeof(float);
     if (smem > 96 * 1024) return (int)cudaErrorInvalidValue;
     float* decay = scratch ? scratch + (size_t)S * max_chunks * heads * (size_t)N * P : nullptr;
     const float inv_tau = 1.f / tau;
-#define GLA_CASE(TT, K, W, pass, chunks)                                                                                    \
-    case K: {                                                                                                              \
+#define GLA_LAUNCH(TT, K, W, C, pass, chunks)                                                                               \
+    {                                                                                                                      \
         static size_t configured = 0;                                                                                      \
         if (smem > 48 * 1024 && smem > configured) {                                                                       \
-            cudaError_t ce = cudaFuncSetAttribute(gla_scan_kernel<TT, K, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t ce = cudaFuncSetAttribute(gla_scan_kernel<TT, K, W, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (ce != cudaSuccess) return (int)ce;                                                                         \
             configured = smem;                                                                                             \
         }                                                                                                                  \
-        err = (int)launch_kernel(gla_scan_kernel<TT, K, W>, dim3(heads * col_blocks, S, chunks), threads, smem, stream, (const TT*)q, q_stride, \
+        err = (int)launch_kernel(gla_scan_kernel<TT, K, W, C>, dim3(heads * col_blocks, S, chunks), threads, smem, stream, (const TT*)q, q_stride, \
                                  (const TT*)k, k_stride, (const TT*)v, v_stride, z, z_stride, z_bias, inv_tau, q_scale, state, \
                                  slot_stride, o, meta, cu_tokens, slots, heads, P, N, R, PB, col_blocks, pass, chunk_len,     \
                                  max_chunks, scratch, decay);                                                              \
-        break;                                                                                                             \
     }
+#define GLA_CASE(TT, K, W, pass, chunks)                                                                                    \
+    case K:                                                                                                                \
+        if (CPT == 4) { if constexpr (K <= 16) GLA_LAUNCH(TT, K, W, 4, pass, chunks) }                                     \
+        else if (CPT == 2) { if constexpr (K <= 32) GLA_LAUNCH(TT, K, W, 2, pass, chunks) }                                \
+        else GLA_LAUNCH(TT, K, W, 1, pass, chunks)                                                                         \
+        break;
 #define GLA_PASS(TT, W, pass, chunks)                                                                                       \
     switch (NPT) { GLA_CASE(TT, 8, W, pass, chunks) GLA_CASE(TT, 16, W, pass, chunks) GLA_CASE(TT, 32, W, pass, chunks) GLA_CASE(TT, 64, W, pass, chunks) }
     int err = 0;
-    if (chunk_len <= 0 || max_chunks <= 1 || !scratch) {
+    if (!chunked) {
         if (dtype == DT_F32) { GLA_PASS(float, true, 0, 1) } else { GLA_PASS(__nv_bfloat16, true, 0, 1) }
         return err;
     }
@@ -222,6 +296,7 @@ extern "C" int gla_scan(const void* q, long long q_stride, const void* k, long l
     if (dtype == DT_F32) { GLA_PASS(float, true, 3, max_chunks) } else { GLA_PASS(__nv_bfloat16, true, 3, max_chunks) }
     return err;
 #undef GLA_PASS
+#undef GLA_LAUNCH
 #undef GLA_CASE
 }
 
