@@ -2,6 +2,8 @@
 // applied head by head, and the rows' preparation (norm of the key/value latent, rotation of the shared key part and
 // of the queries' rotated parts, the cached vector written to its page, the queries laid out for the attention
 // kernels).  Storage is float32 or bfloat16, arithmetic float32.
+#include <algorithm>
+
 #include "common.cuh"
 
 // out[t] = x[t] * rsqrt(mean(x[t]^2) + eps) * w over n elements; x is a slice of a wider row (x_stride from row to row).
@@ -116,15 +118,31 @@ extern "C" int head_linear(const void* x, long long xs_t, long long xs_h, const 
                               meta, K, N, wvec);
 }
 
-// y[t, h, n] *= sigmoid(gate[t, h, n]) for a product that a library made (same slices as above).
+// y[t, h, n] *= sigmoid(gate[t, h, n]) for a product that a library made (same slices as above).  ``vec``: every head's
+// slice of y and of gate starts on 16 bytes and N is a multiple of 16 bytes' worth of elements; a thread then maps 16 bytes.
 template <typename T>
 __global__ void __launch_bounds__(256)
 sigmoid_gate_kernel(T* __restrict__ y, long long ys_t, long long ys_h, const T* __restrict__ gate, long long gs_t,
-                    long long gs_h, const int* __restrict__ meta, int heads, int N) {
+                    long long gs_h, const int* __restrict__ meta, int heads, int N, int vec) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     if (t >= meta[META_NUM_TOKENS]) return;
+    if (vec) {
+        constexpr int V = 16 / (int)sizeof(T);
+        for (int idx = threadIdx.x * V; idx < heads * N; idx += blockDim.x * V) {
+            const int h = idx / N, n = idx % N;
+            uint4 gv = *reinterpret_cast<const uint4*>(gate + (size_t)t * gs_t + (size_t)h * gs_h + n);
+            uint4* at = reinterpret_cast<uint4*>(y + (size_t)t * ys_t + (size_t)h * ys_h + n);
+            uint4 yv = *at;
+            const T* ge = reinterpret_cast<const T*>(&gv);
+            T* ye = reinterpret_cast<T*>(&yv);
+#pragma unroll
+            for (int i = 0; i < V; ++i) ye[i] = from_float<T>(to_float(ye[i]) / (1.f + expf(-to_float(ge[i]))));
+            *at = yv;
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < heads * N; idx += blockDim.x) {
         const int h = idx / N, n = idx % N;
         const float g = to_float(gate[(size_t)t * gs_t + (size_t)h * gs_h + n]);
@@ -136,11 +154,15 @@ sigmoid_gate_kernel(T* __restrict__ y, long long ys_t, long long ys_h, const T* 
 extern "C" int sigmoid_gate(void* y, long long ys_t, long long ys_h, const void* gate, long long gs_t, long long gs_h,
                             int dtype, const int* meta, int T, int heads, int N, cudaStream_t stream) {
     if (T <= 0) return 0;
+    const long long V = dtype == DT_F32 ? 4 : 8;
+    const int vec = N % V == 0 && ys_t % V == 0 && ys_h % V == 0 && gs_t % V == 0 && gs_h % V == 0 &&
+                    ((uintptr_t)y | (uintptr_t)gate) % 16 == 0;
+    const int threads = (int)std::min<long long>(256, std::max<long long>(32, ((long long)heads * N / (vec ? V : 1) + 31) / 32 * 32));
     if (dtype == DT_F32)
-        return (int)launch_kernel(sigmoid_gate_kernel<float>, T, 256, 0, stream, (float*)y, ys_t, ys_h, (const float*)gate, gs_t,
-                                  gs_h, meta, heads, N);
-    return (int)launch_kernel(sigmoid_gate_kernel<__nv_bfloat16>, T, 256, 0, stream, (__nv_bfloat16*)y, ys_t, ys_h,
-                              (const __nv_bfloat16*)gate, gs_t, gs_h, meta, heads, N);
+        return (int)launch_kernel(sigmoid_gate_kernel<float>, T, threads, 0, stream, (float*)y, ys_t, ys_h, (const float*)gate, gs_t,
+                                  gs_h, meta, heads, N, vec);
+    return (int)launch_kernel(sigmoid_gate_kernel<__nv_bfloat16>, T, threads, 0, stream, (__nv_bfloat16*)y, ys_t, ys_h,
+                              (const __nv_bfloat16*)gate, gs_t, gs_h, meta, heads, N, vec);
 }
 
 // ----------------------------------------------------------------------------- the rows of latent attention

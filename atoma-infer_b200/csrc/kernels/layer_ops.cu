@@ -305,6 +305,8 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
     const int NQ = nq * d, NK = nkv * d, NV = nkv * dv;
     int half = rot / 2;
     float* trig = vals + NQ + NK;
+    float* part = trig + rot;              // with head_norm: the sum of squares of every four neighbouring values
+    float* hinv = part + (NQ + NK) / 4;    // ... and 1 / root mean square of every head
     const int pos = live ? positions[t] : 0;
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
     int page = 0;
@@ -327,15 +329,17 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
         float sq = 0.f, sk = 0.f;
         if (vec4) {  // four values a thread (d, dv, dp and rot / 2 multiples of 4, buffers on 16 bytes)
             for (int i = threadIdx.x * 4; i < NQ + NK; i += blockDim.x * 4) {
-                float v[4], bv[4] = {0.f, 0.f, 0.f, 0.f};
+                float v[4], bv[4] = {0.f, 0.f, 0.f, 0.f}, four = 0.f;
                 load4(row + i, v);
                 if (bias) load4(bias + i, bv);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     v[k] += bv[k];
                     if (i < NQ) sq = fmaf(v[k], v[k], sq); else sk = fmaf(v[k], v[k], sk);
+                    four = fmaf(v[k], v[k], four);
                 }
                 store4(vals + i, v);
+                if (head_norm) part[i >> 2] = four;
             }
         } else {
             for (int i = threadIdx.x; i < NQ + NK; i += blockDim.x) {
@@ -353,7 +357,17 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
         } else {
             __syncthreads();
         }
-        if (head_norm) {
+        const bool head_inv = head_norm && vec4;
+        if (head_inv) {
+            // A rotation leaves a pair's sum of squares as it is, so a head's is that of its values before the rotation:
+            // a thread a head adds the fours' sums in ascending order; what follows rotates and multiplies.
+            for (int h = threadIdx.x; h < nq + nkv; h += blockDim.x) {
+                float ss = 0.f;
+                for (int j = 0; j < d / 4; ++j) ss += part[h * (d / 4) + j];
+                hinv[h] = rsqrtf(ss / (float)d + eps);
+            }
+            __syncthreads();
+        } else if (head_norm) {
             // a warp a head: the rotation in place, the head's sum of squares over the lanes in a fixed order, the division;
             // what follows writes the heads out as they are
             const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -394,7 +408,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
                     const bool is_q = h < nq;
                     T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
                     const int base = h * d, nb = is_q ? base : base - NQ;  // k heads follow the q heads in vals
-                    const float inv = is_q ? inv_q : inv_k;
+                    const float inv = head_inv ? hinv[h] : (is_q ? inv_q : inv_k);
                     const TP* nw = is_q ? q_norm : k_norm;
                     auto normed4 = [&](int j, float (&o)[4]) {
                         float wv[4] = {1.f, 1.f, 1.f, 1.f};
@@ -497,7 +511,7 @@ extern "C" int qkv_prepare(const void* qkv, long long qkv_stride, int dtype, con
                            int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (head_norm && (q_norm || k_norm)) return (int)cudaErrorInvalidValue;
-    const size_t smem = ((size_t)(nq + nkv) * d + rot) * sizeof(float);
+    const size_t smem = ((size_t)(nq + nkv) * d + rot + (head_norm ? (size_t)(nq + nkv) * (d / 4 + 1) : 0)) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     // Few tokens: 256 threads a block, the shortest path through a token.  Many: 128, so that more blocks, each at another
     // of its phases, share a multiprocessor (16,384 tokens of 32 + 8 heads of 64: 143 -> 107 us).

@@ -285,3 +285,25 @@ def test_weighted_sum_into_the_stream_and_two_norms(rts, H):
         assert torch.allclose(out.cpu().double(), PB.rms_norm(s, w1.double(), 1e-5), atol=tol * 4)
         assert torch.allclose(out2.cpu().double(), PB.rms_norm(s, w2.double(), 1e-5), atol=tol * 4)
     rt.ops.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,N,pad", [(32, 64, 0), (6, 24, 8), (3, 20, 0), (5, 8, 3)])
+def test_output_gate_on_slices_of_wider_rows(rts, dtype, heads, N, pad):
+    """y[t, h, :N] *= sigmoid(gate[t, h, :N]) in place, y a slice of heads padded to N + pad and the gate the last columns of
+    wider rows: slices that start on 16 bytes (sixteen bytes a thread) and slices that do not (an element a thread)."""
+    rt = rts[dtype]
+    g = torch.Generator().manual_seed(N)
+    T, lead = 37, 40 if pad != 3 else 5
+    ctx, _ = K.make_context(rt, [(0, T)], 16, [[1, 2, 3]])
+    y_full = torch.randn(T, heads, N + pad, generator=g).to(rt.dtype).to(rt.device)
+    rows = (3 * torch.randn(T, lead + heads * N, generator=g)).to(rt.dtype).to(rt.device)
+    before = y_full.clone()
+    gate = rows[:, lead:].view(T, heads, N)
+    rt.ops.sigmoid_gate(y_full[:, :, :N], gate, ctx.meta)
+    rt.ops.check_status()
+    want = before.double()
+    want[:, :, :N] *= torch.sigmoid(gate.double())
+    tol = 1e-6 if dtype == "float32" else 1e-2
+    assert torch.allclose(y_full.double(), want, atol=tol, rtol=tol)
+    assert torch.equal(y_full[:, :, N:], before[:, :, N:])
