@@ -44,15 +44,18 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
 // columns in registers (a row's k, a and q are loaded once for all of them); R threads (a power of two, neighbouring
 // lanes) share the columns; rows beyond N see k = q = 0 and stay zero.  P is a multiple of CPT.  An output is the sum of
 // the even rows' products plus the sum of the odd rows', each in ascending order, then the R threads' sums by halving.
+template <typename T>
+struct alignas(4 * sizeof(T)) Raw4 { T x[4]; };  // four stored values, loaded at once
+
 template <typename T, int NPT, bool WRITE_O, int CPT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, NPT <= 16 ? 2 : 1)
 gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k, long long k_stride,
                 const T* __restrict__ v, long long v_stride, const float* __restrict__ z, long long z_stride,
                 const float* __restrict__ z_bias, float inv_tau, float q_scale, float* __restrict__ state,
                 long long slot_stride, float* __restrict__ o, const int* __restrict__ meta,
                 const int* __restrict__ cu_tokens, const int* __restrict__ slots, int heads, int P, int N, int R, int PB,
                 int col_blocks, int pass, int chunk_len, int max_chunks, float* __restrict__ scratch,
-                float* __restrict__ decay) {
+                float* __restrict__ decay, int vec) {
     extern __shared__ __align__(16) float sm[];
     const int SL = R > 1 ? NPT + 4 : NPT, NL = R * NPT, NP = R * SL;  // row n lies at (n / NPT) * SL + n % NPT
     float* qs = sm;                     // [REC_TT][NP]
@@ -93,6 +96,65 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
     for (int tb = t0; tb < t1; tb += REC_TT) {
         const int nt = min(REC_TT, t1 - tb);
         __syncthreads();  // the previous tile is no longer read
+        if (CPT > 1 && vec) {  // (the one-column kernels, which run steps of few tokens, stay small: more blocks at a time)
+            // four neighbouring rows (or columns) an item, two items a thread at a time, every load ahead of the first use
+            const int QI = NL / 4, qitems = nt * QI, VI = PB / 4, vitems = nt * VI;
+            for (int i0 = tid; i0 < qitems; i0 += 2 * blockDim.x) {
+                Raw4<T> rq[2], rk[2];
+                float4 rz[2];
+                int at[2], hn4[2];
+                bool in[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int idx = i0 + u * blockDim.x, tt = idx / QI, n = (idx % QI) * 4;
+                    at[u] = idx < qitems ? tt * NP + (n / NPT) * SL + n % NPT : -1;
+                    in[u] = idx < qitems && n < N;
+                    hn4[u] = h * N + n;
+                    if (in[u]) {
+                        const size_t t = (size_t)(tb + tt), hn = (size_t)h * N + n;
+                        rq[u] = *reinterpret_cast<const Raw4<T>*>(q + t * q_stride + hn);
+                        rk[u] = *reinterpret_cast<const Raw4<T>*>(k + t * k_stride + hn);
+                        rz[u] = *reinterpret_cast<const float4*>(z + t * z_stride + hn);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (at[u] < 0) continue;
+                    float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f), k4 = q4, a4 = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (in[u]) {
+                        // (the bias is the same for every token: it stays in the first-level cache)
+                        const float4 rb = z_bias ? *reinterpret_cast<const float4*>(z_bias + hn4[u]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        q4 = make_float4(to_float(rq[u].x[0]) * q_scale, to_float(rq[u].x[1]) * q_scale, to_float(rq[u].x[2]) * q_scale,
+                                         to_float(rq[u].x[3]) * q_scale);
+                        k4 = make_float4(to_float(rk[u].x[0]), to_float(rk[u].x[1]), to_float(rk[u].x[2]), to_float(rk[u].x[3]));
+                        a4 = make_float4(expf(-softplus_f(-(rz[u].x + rb.x)) * inv_tau), expf(-softplus_f(-(rz[u].y + rb.y)) * inv_tau),
+                                         expf(-softplus_f(-(rz[u].z + rb.z)) * inv_tau), expf(-softplus_f(-(rz[u].w + rb.w)) * inv_tau));
+                    }
+                    *reinterpret_cast<float4*>(qs + at[u]) = q4;
+                    *reinterpret_cast<float4*>(ks + at[u]) = k4;
+                    *reinterpret_cast<float4*>(as + at[u]) = a4;
+                }
+            }
+            for (int i0 = tid; i0 < vitems; i0 += 2 * blockDim.x) {
+                Raw4<T> rv[2];
+                int at[2];
+                bool in[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int idx = i0 + u * blockDim.x, tt = idx / VI, pc = cb * PB + (idx % VI) * 4;
+                    at[u] = idx < vitems ? idx * 4 : -1;
+                    in[u] = idx < vitems && pc < P;
+                    if (in[u]) rv[u] = *reinterpret_cast<const Raw4<T>*>(v + (size_t)(tb + tt) * v_stride + (size_t)h * P + pc);
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (at[u] < 0) continue;
+                    *reinterpret_cast<float4*>(vs + at[u]) =
+                        in[u] ? make_float4(to_float(rv[u].x[0]), to_float(rv[u].x[1]), to_float(rv[u].x[2]), to_float(rv[u].x[3]))
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+        } else {
         for (int idx = tid; idx < nt * NL; idx += blockDim.x) {
             const int tt = idx / NL, n = idx % NL, at = tt * NP + (n / NPT) * SL + n % NPT;
             const size_t t = (size_t)(tb + tt);
@@ -111,6 +173,7 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
         for (int idx = tid; idx < nt * PB; idx += blockDim.x) {
             const int tt = idx / PB, pc = cb * PB + idx % PB;
             vs[idx] = pc < P ? to_float(v[(size_t)(tb + tt) * v_stride + (size_t)h * P + pc]) : 0.f;
+        }
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
@@ -256,6 +319,11 @@ extern "C" int gla_scan(const void* q, long long q_stride, const void* k, long l
     };
     const int CPT = !chunked ? 1 : (NPT <= 16 && aligned(4) ? 4 : (NPT <= 32 && aligned(2) ? 2 : 1));
     rec_geometry(N, P, &NPT, &R, &PB, CPT);
+    // tiles of q, k, decay logits and v in items of four: rows and columns in fours, every row's slice on its vector's boundary
+    const uintptr_t esz = dtype == DT_F32 ? 4 : 2;
+    const int vec = N % 4 == 0 && P % 4 == 0 && PB % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 &&
+                    z_stride % 4 == 0 && ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % (4 * esz) == 0 &&
+                    ((uintptr_t)z | (uintptr_t)z_bias) % 16 == 0;
     const int col_blocks = (P + PB - 1) / PB, threads = ((PB / CPT * R + 31) / 32) * 32;
     const size_t smem = (size_t)(3 * REC_TT * R * (R > 1 ? NPT + 4 : NPT) + REC_TT * PB) * sizeof(float);
     if (smem > 96 * 1024) return (int)cudaErrorInvalidValue;
@@ -272,7 +340,7 @@ extern "C" int gla_scan(const void* q, long long q_stride, const void* k, long l
         err = (int)launch_kernel(gla_scan_kernel<TT, K, W, C>, dim3(heads * col_blocks, S, chunks), threads, smem, stream, (const TT*)q, q_stride, \
                                  (const TT*)k, k_stride, (const TT*)v, v_stride, z, z_stride, z_bias, inv_tau, q_scale, state, \
                                  slot_stride, o, meta, cu_tokens, slots, heads, P, N, R, PB, col_blocks, pass, chunk_len,     \
-                                 max_chunks, scratch, decay);                                                              \
+                                 max_chunks, scratch, decay, vec);                                                         \
     }
 #define GLA_CASE(TT, K, W, pass, chunks)                                                                                    \
     case K:                                                                                                                \
