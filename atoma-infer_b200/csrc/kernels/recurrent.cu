@@ -404,8 +404,18 @@ extern "C" int head_norm_gate(const float* o, const void* g, int dtype, long lon
 // u [T, inner] (after convolution and activation), zg [T, inner] (the gate's input): slices of wider rows; dt_raw float32
 // [T, inner] (softplus(dt_raw + dt_bias) is taken here); B at bc, C at bc + N of a row of bc_stride elements; a_log [inner, N];
 // state [slots][inner][N]; out [T, inner] = (sum_n S[c, n] C_n + D_c u_c) * silu(zg_c).
-// One block per (channel block, entry[, chunk]).  Thread (c, r) keeps NPT states n = r * NPT .. of channel c.
+// One block per (channel block, entry[, chunk]).  Thread (c, r) keeps NPT states n = r * NPT .. of channel c, as pairs of
+// neighbouring states that one two-wide instruction updates.  y is the even states' sum plus the odd states', each in
+// ascending order, then the R threads' sums by halving.
 #define LOG2E_F 1.4426950408889634f
+
+// 2^x for x <= 0 by the hardware's instruction alone (what exp2f runs for arguments in the normal range; a result below
+// the smallest normal number is zero, which a decay of that size is for every state that float32 holds).
+__device__ __forceinline__ float ex2_nonpositive(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 template <typename T, int NPT, bool WRITE_Y>
 __global__ void __launch_bounds__(256)
@@ -427,11 +437,12 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
     const int tid = threadIdx.x, cl = tid / R, r = tid % R, c = blockIdx.x * CPB + cl;
     const bool real = cl < CPB && c < inner;
     // the weights come before the wait: no kernel writes them
-    float A2[NPT];
+    float2 A2[NPT / 2];  // A log2(e), pairs of neighbouring states
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
         const int n = r * NPT + i;
-        A2[i] = (real && n < N) ? -expf(a_log[(size_t)c * N + n]) * LOG2E_F : 0.f;
+        const float a = (real && n < N) ? -expf(a_log[(size_t)c * N + n]) * LOG2E_F : 0.f;
+        if (i & 1) A2[i / 2].y = a; else A2[i / 2].x = a;
     }
     const float dskip = real ? d_skip[c] : 0.f;
     pdl_launch_dependents();
@@ -445,11 +456,12 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
     float* slot_state = state + (size_t)slots[e] * slot_stride;
     float* chunk_state = scratch ? scratch + ((size_t)e * max_chunks + ch) * HS : nullptr;
     const float* init = pass == 0 ? slot_state : (pass == 3 ? chunk_state : nullptr);
-    float S[NPT];
+    float2 S[NPT / 2];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
         const int n = r * NPT + i;
-        S[i] = (init && real && n < N) ? init[(size_t)c * N + n] : 0.f;
+        const float s0 = (init && real && n < N) ? init[(size_t)c * N + n] : 0.f;
+        if (i & 1) S[i / 2].y = s0; else S[i / 2].x = s0;
     }
     float dt_sum = 0.f;
     for (int tb = t0; tb < t1; tb += REC_TT) {
@@ -475,22 +487,23 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
             const float dx = step * uv;
             const float* Bt = Bs + tt * NP + r * SL;
             const float* Ct = Cs + tt * NP + r * SL;
-            float acc = 0.f;
+            const float2 st2 = make_float2(step, step), dx2 = make_float2(dx, dx);
+            float2 acc2 = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int i = 0; i < NPT; i += 4) {
-                const float4 b4 = *reinterpret_cast<const float4*>(Bt + i);
-                S[i] = fmaf(exp2f(step * A2[i]), S[i], dx * b4.x);
-                S[i + 1] = fmaf(exp2f(step * A2[i + 1]), S[i + 1], dx * b4.y);
-                S[i + 2] = fmaf(exp2f(step * A2[i + 2]), S[i + 2], dx * b4.z);
-                S[i + 3] = fmaf(exp2f(step * A2[i + 3]), S[i + 3], dx * b4.w);
+            for (int i = 0; i < NPT / 2; i += 2) {  // two pairs of neighbouring states a round
+                const float4 b4 = *reinterpret_cast<const float4*>(Bt + 2 * i);
+                float2 ea = mul2(st2, A2[i]), eb = mul2(st2, A2[i + 1]);
+                ea = make_float2(ex2_nonpositive(ea.x), ex2_nonpositive(ea.y));
+                eb = make_float2(ex2_nonpositive(eb.x), ex2_nonpositive(eb.y));
+                S[i] = fma2(ea, S[i], mul2(dx2, make_float2(b4.x, b4.y)));
+                S[i + 1] = fma2(eb, S[i + 1], mul2(dx2, make_float2(b4.z, b4.w)));
                 if (WRITE_Y) {
-                    const float4 c4 = *reinterpret_cast<const float4*>(Ct + i);
-                    acc = fmaf(S[i], c4.x, acc);
-                    acc = fmaf(S[i + 1], c4.y, acc);
-                    acc = fmaf(S[i + 2], c4.z, acc);
-                    acc = fmaf(S[i + 3], c4.w, acc);
+                    const float4 c4 = *reinterpret_cast<const float4*>(Ct + 2 * i);
+                    acc2 = fma2(S[i], make_float2(c4.x, c4.y), acc2);
+                    acc2 = fma2(S[i + 1], make_float2(c4.z, c4.w), acc2);
                 }
             }
+            float acc = acc2.x + acc2.y;  // the even states' sum plus the odd states'
             if (WRITE_Y) {
                 for (int s = R >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
                 if (real && r == 0) {
@@ -506,7 +519,7 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
             const int n = r * NPT + i;
-            if (n < N) fin[(size_t)c * N + n] = S[i];
+            if (n < N) fin[(size_t)c * N + n] = (i & 1) ? S[i / 2].y : S[i / 2].x;
         }
     }
     if (pass == 1 && real && r == 0) dt_sums[((size_t)e * max_chunks + ch) * inner + c] = dt_sum;
