@@ -406,7 +406,8 @@ extern "C" int head_norm_gate(const float* o, const void* g, int dtype, long lon
 // state [slots][inner][N]; out [T, inner] = (sum_n S[c, n] C_n + D_c u_c) * silu(zg_c).
 // One block per (channel block, entry[, chunk]).  Thread (c, r) keeps NPT states n = r * NPT .. of channel c, as pairs of
 // neighbouring states that one two-wide instruction updates.  y is the even states' sum plus the odd states', each in
-// ascending order, then the R threads' sums by halving.
+// ascending order, then the R threads' sums by halving.  B and C of 16 tokens are staged in shared memory; the channel's
+// own u, step size and gate input of those tokens go straight into the thread's registers.
 #define LOG2E_F 1.4426950408889634f
 
 // 2^x for x <= 0 by the hardware's instruction alone (what exp2f runs for arguments in the normal range; a result below
@@ -430,9 +431,6 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
     const int SL = R > 1 ? NPT + 4 : NPT, NL = R * NPT, NP = R * SL;
     float* Bs = sm;                      // [REC_TT][NP]
     float* Cs = Bs + REC_TT * NP;        // [REC_TT][NP]
-    float* us = Cs + REC_TT * NP;        // [REC_TT][CPB]
-    float* ds = us + REC_TT * CPB;       // [REC_TT][CPB] step sizes
-    float* zs = ds + REC_TT * CPB;       // [REC_TT][CPB]
     const int e = blockIdx.y, ch = blockIdx.z;
     const int tid = threadIdx.x, cl = tid / R, r = tid % R, c = blockIdx.x * CPB + cl;
     const bool real = cl < CPB && c < inner;
@@ -444,7 +442,7 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
         const float a = (real && n < N) ? -expf(a_log[(size_t)c * N + n]) * LOG2E_F : 0.f;
         if (i & 1) A2[i / 2].y = a; else A2[i / 2].x = a;
     }
-    const float dskip = real ? d_skip[c] : 0.f;
+    const float dskip = real ? d_skip[c] : 0.f, dtb = real ? dt_bias[c] : 0.f;
     pdl_launch_dependents();
     pdl_wait();
     if (e >= meta[META_NUM_ENTRIES]) return;
@@ -466,6 +464,18 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
     float dt_sum = 0.f;
     for (int tb = t0; tb < t1; tb += REC_TT) {
         const int nt = min(REC_TT, t1 - tb);
+        // this thread's channel of the tile's tokens, straight into registers: every load is on its way before the
+        // first is used (the R threads of a channel read the same addresses)
+        T ur[REC_TT], zr[REC_TT];
+        float dr[REC_TT];
+#pragma unroll
+        for (int tt = 0; tt < REC_TT; ++tt) {
+            const bool in = real && tt < nt;
+            const size_t t = (size_t)(tb + tt);
+            ur[tt] = in ? u[t * u_stride + c] : from_float<T>(0.f);
+            dr[tt] = in ? dt_raw[t * inner + c] : 0.f;
+            if (WRITE_Y) zr[tt] = in ? zg[t * z_stride + c] : from_float<T>(0.f);
+        }
         __syncthreads();
         for (int idx = tid; idx < nt * NL; idx += blockDim.x) {
             const int tt = idx / NL, n = idx % NL, at = tt * NP + (n / NPT) * SL + n % NPT;
@@ -473,17 +483,11 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
             Bs[at] = n < N ? to_float(row[n]) : 0.f;
             Cs[at] = n < N ? to_float(row[N + n]) : 0.f;
         }
-        for (int idx = tid; idx < nt * CPB; idx += blockDim.x) {
-            const int tt = idx / CPB, cc = blockIdx.x * CPB + idx % CPB;
-            const size_t t = (size_t)(tb + tt);
-            const bool in = cc < inner;
-            us[idx] = in ? to_float(u[t * u_stride + cc]) : 0.f;
-            ds[idx] = in ? softplus_f(dt_raw[t * inner + cc] + dt_bias[cc]) : 0.f;
-            zs[idx] = (in && WRITE_Y) ? to_float(zg[t * z_stride + cc]) : 0.f;
-        }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float uv = cl < CPB ? us[tt * CPB + cl] : 0.f, step = cl < CPB ? ds[tt * CPB + cl] : 0.f;
+#pragma unroll
+        for (int tt = 0; tt < REC_TT; ++tt) {
+            if (tt >= nt) break;
+            const float uv = to_float(ur[tt]), step = real ? softplus_f(dr[tt] + dtb) : 0.f;
             const float dx = step * uv;
             const float* Bt = Bs + tt * NP + r * SL;
             const float* Ct = Cs + tt * NP + r * SL;
@@ -508,7 +512,7 @@ selective_scan_kernel(const T* __restrict__ u, long long u_stride, const float* 
                 for (int s = R >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
                 if (real && r == 0) {
                     const float y = fmaf(dskip, uv, acc);
-                    out[(size_t)(tb + tt) * inner + c] = from_float<T>(y * silu_f(zs[tt * CPB + cl]));
+                    out[(size_t)(tb + tt) * inner + c] = from_float<T>(y * silu_f(to_float(zr[tt])));
                 }
             }
             dt_sum += step;
@@ -563,7 +567,7 @@ extern "C" int selective_scan(const void* u, long long u_stride, const float* dt
     if (!rec_geometry(N, inner, &NPT, &R, &CPB)) return (int)cudaErrorInvalidValue;
     if (CPB * R > 128) CPB = 128 / R > 0 ? 128 / R : 1;  // 128 threads a block: more blocks for few requests
     const int blocks = (inner + CPB - 1) / CPB, threads = ((CPB * R + 31) / 32) * 32;
-    const size_t smem = (size_t)(2 * REC_TT * R * (R > 1 ? NPT + 4 : NPT) + 3 * REC_TT * CPB) * sizeof(float);
+    const size_t smem = (size_t)(2 * REC_TT * R * (R > 1 ? NPT + 4 : NPT)) * sizeof(float);
     if (smem > 96 * 1024) return (int)cudaErrorInvalidValue;
     float* dt_sums = scratch ? scratch + (size_t)S * max_chunks * (size_t)inner * N : nullptr;
 #define SEL_CASE(TT, K, W, pass, chunks)                                                                                    \

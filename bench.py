@@ -269,17 +269,17 @@ def tutezen_config(size: str, layers: int, vocab: int = 32768, window: int = 102
 
 def bumolix_config(size: str, layers: int, vocab: int = 32768, chunk: int = 1024):
     """A Bumolix configuration of the width, heads and feed-forward size of ``size``: layers whose mixer is attention
-    (chunks of ``chunk``, half of a head rotated, positions stretched by 4) beside gated linear attention (width / 256
+    (chunks of ``chunk``, half of a head rotated, positions stretched by 8) beside gated linear attention (width / 256
     heads of 128 key channels and 256 value channels) alternate with selective-scan layers (twice the width inside, 16
     states a channel, 4 taps, step sizes through width / 16); every layer has the dense feed-forward."""
     H, I, nq, nkv, d = DESIGN_SIZES[size]
     left = {"heads": nq, "kv_heads": nkv, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": chunk},
-            "rot": {"dims": d // 2, "base": 500000.0, "scaling": {"factor": 4.0}}}
-    right = {"heads": H // 256, "dim": 128, "vdim": 256, "tau": 16.0}
+            "rot": {"dims": d // 2, "base": 1000000.0, "scaling": {"factor": 8.0}}}
+    right = {"heads": H // 256, "dim": 128, "vdim": 256, "tau": 8.0}
     mlp = {"kind": "dense", "ff": I}
-    pair = [{"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.9}, "mlp": mlp},
+    pair = [{"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.5, "right_scale": 1.25}, "mlp": mlp},
             {"type": "mamba1", "mixer": {"inner": 2 * H, "state": 16, "dt_rank": H // 16, "conv": 4}, "mlp": mlp}]
-    return {"architecture": "Bumolix", "vocab": vocab, "width": H, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+    return {"architecture": "Bumolix", "vocab": vocab, "width": H, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
             "layers": [pair[i % 2] for i in range(layers)]}
 
 
@@ -636,7 +636,7 @@ def bumolix_kernels(rt, hbm, median_ms) -> None:
         twice = 2 if T >= 128 else 1  # (chunks of time run twice)
         cases = [
             ("bumolix: weighted pending sum of three + two RMSNorms",
-             lambda: ops.sum_rmsnorm(resid, PendingSum((a, b, c), 0.7, factors=(0.6, 0.9, 1.0)), w, 1e-5, out, ctx.meta, T, second=(w, 1e-5, out2)),
+             lambda: ops.sum_rmsnorm(resid, PendingSum((a, b, c), 0.5, factors=(0.5, 1.25, 1.0)), w, 1e-5, out, ctx.meta, T, second=(w, 1e-5, out2)),
              T * H * (4 + 3 * 2 + 4 + 2 * 2), None),
             ("tutezen: pending sum of two + RMSNorm", lambda: ops.sum_rmsnorm(resid, PendingSum((a, b), 0.5), w, 1e-5, out, ctx.meta, T),
              T * H * (4 + 2 + 2 + 4 + 2), None),
@@ -651,7 +651,7 @@ def bumolix_kernels(rt, hbm, median_ms) -> None:
             ("bumolix: output gate (sigmoid, in place)", lambda: ops.sigmoid_gate(att, gate, ctx.meta), T * nq * d * 2 * 3, None),
             ("bumolix: gated linear attention, 8 x 128 x 256 (float32 FMA)",
              lambda: ops.gla_scan(g_proj[:, :gh * gN], g_proj[:, gh * gN:2 * gh * gN], g_proj[:, 2 * gh * gN:2 * gh * gN + gh * gP], g_z, g_bias,
-                                  16.0, gN ** -0.5, g_state, ctx, g_o, heads=gh, dim=gN, vdim=gP),
+                                  8.0, gN ** -0.5, g_state, ctx, g_o, heads=gh, dim=gN, vdim=gP),
              T * (2 * gh * gN * 2 + gh * gP * 2 + gh * gN * 4 + gh * gP * 4) + 2 * S * gh * gN * gP * 4, 6.0 * T * gh * gN * gP * twice),
             ("tutezen: recurrence, 64 x 128 x 64 (float32 FMA)",
              lambda: ops.ssm_scan(t_xbc, t_proj[:, t_inner + tC:], hv, hv * 0, hv, t_state, ctx, t_y, heads=th, head_dim=tP, nstate=tN, groups=tG),
