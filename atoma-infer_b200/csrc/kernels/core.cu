@@ -421,7 +421,8 @@ __global__ void __launch_bounds__(ATTN_THREADS)
 attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ cache, CacheLayout L,
                     const int* __restrict__ meta, int group, const int* __restrict__ token_entry,
                     const int* __restrict__ positions, T* __restrict__ out, int nq, int window, int chunk, int sink,
-                    const float* __restrict__ sink_values, float scale, int num_pages, int* __restrict__ status) {
+                    const float* __restrict__ sink_values, float scale, int num_pages, int keep_first, float softcap,
+                    const float* __restrict__ slopes, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait();
     int t = blockIdx.x, h = blockIdx.y;
@@ -443,8 +444,11 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
     float acc[ATTN_ACC] = {};  // head sizes up to ATTN_ACC * ATTN_THREADS
     int kstart = window > 0 ? max(0, p - window + 1) : 0;
     if (chunk > 0) kstart = max(kstart, p - p % chunk);
-    for (int k0 = kstart; k0 <= p; k0 += ATTN_KT) {
-        const int n = min(ATTN_KT, p - k0 + 1);
+    // kept first tokens: the keys 0 .. kept - 1 are seen as well, in tiles of their own ahead of the window's
+    const int kept = window > 0 && chunk <= 0 ? min(keep_first, kstart) : 0;
+    const float slope = slopes ? slopes[h] : 0.f;
+    for (int k0 = kept > 0 ? 0 : kstart; k0 <= p; k0 = (k0 < kstart && k0 + ATTN_KT >= kept) ? kstart : k0 + ATTN_KT) {
+        const int n = k0 < kstart ? min(ATTN_KT, kept - k0) : min(ATTN_KT, p - k0 + 1);
         __syncthreads();  // the previous tile's values are no longer read
         for (int idx = tid; idx < n * d; idx += ATTN_THREADS) {
             int j = idx / d, i = idx % d, pos = k0 + j;
@@ -462,6 +466,8 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
             float dot = 0.f;
             for (int i = 0; i < d; ++i) dot = fmaf(qs[i], tile[tid * ld + i], dot);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+            s -= slope * (float)(p - (k0 + tid));  // a bias by distance: slope * (i - j)
         }
         float m_new = fmaxf(m, block_max(s, red));
         float pj = tid < n ? expf(s - m_new) : 0.f;
@@ -496,11 +502,28 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
     }
 }
 
+extern "C" int attn_generic_scores(const void* q, int q_stride, const void* cache, int dtype, const int* meta, int group,
+                                   const int* token_entry, const int* positions, void* out, int T, int nq, int nkv, int d,
+                                   int page_size, int num_pages, int window, int chunk, int sink, const float* sink_values,
+                                   float scale, int keep_first, float softcap, const float* slopes, int* status,
+                                   cudaStream_t stream);
+
 // sink_values (one float per query head, or null): the sink's score per head instead of 0.
 extern "C" int attn_generic_sinks(const void* q, int q_stride, const void* cache, int dtype, const int* meta, int group,
                                   const int* token_entry, const int* positions, void* out, int T, int nq, int nkv, int d,
                                   int page_size, int num_pages, int window, int chunk, int sink, const float* sink_values,
                                   float scale, int* status, cudaStream_t stream) {
+    return attn_generic_scores(q, q_stride, cache, dtype, meta, group, token_entry, positions, out, T, nq, nkv, d, page_size,
+                               num_pages, window, chunk, sink, sink_values, scale, 0, 0.f, nullptr, status, stream);
+}
+
+// keep_first (with a window): the first keep_first keys stay visible behind the window.  softcap > 0: a score s becomes
+// softcap * tanh(s / softcap).  slopes (one float per query head, or null): slopes[h] * (i - j) is taken off the score.
+extern "C" int attn_generic_scores(const void* q, int q_stride, const void* cache, int dtype, const int* meta, int group,
+                                   const int* token_entry, const int* positions, void* out, int T, int nq, int nkv, int d,
+                                   int page_size, int num_pages, int window, int chunk, int sink, const float* sink_values,
+                                   float scale, int keep_first, float softcap, const float* slopes, int* status,
+                                   cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d > ATTN_ACC * ATTN_THREADS) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, d};
@@ -517,7 +540,7 @@ extern "C" int attn_generic_sinks(const void* q, int q_stride, const void* cache
         }
         return (int)launch_kernel(attn_generic_kernel<float>, grid, ATTN_THREADS, smem, stream, (const float*)q, q_stride,
                                   (const float*)cache, L, meta, group, token_entry, positions, (float*)out, nq, window, chunk, sink,
-                                  sink_values, scale, num_pages, status);
+                                  sink_values, scale, num_pages, keep_first, softcap, slopes, status);
     } else {
         if (smem > configured_bf16) {
             e = cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -526,7 +549,8 @@ extern "C" int attn_generic_sinks(const void* q, int q_stride, const void* cache
         }
         return (int)launch_kernel(attn_generic_kernel<__nv_bfloat16>, grid, ATTN_THREADS, smem, stream,
                                   (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, L, meta, group, token_entry,
-                                  positions, (__nv_bfloat16*)out, nq, window, chunk, sink, sink_values, scale, num_pages, status);
+                                  positions, (__nv_bfloat16*)out, nq, window, chunk, sink, sink_values, scale, num_pages, keep_first, softcap,
+                                  slopes, status);
     }
 }
 

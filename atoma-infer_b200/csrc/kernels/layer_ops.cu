@@ -294,7 +294,8 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
                    const float* __restrict__ inv_freq, int rot, const T* __restrict__ v_first,
                    const float* __restrict__ v_lambda, T* __restrict__ v_out, T* __restrict__ q_out,
                    T* __restrict__ cache, int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages,
-                   int store_kv, int vec4, int head_norm, int* __restrict__ status) {
+                   int store_kv, int vec4, int head_norm, int interleaved, float qt_coef, int qt_every,
+                   int* __restrict__ status) {
     // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token
     extern __shared__ __align__(16) float vals[];
     __shared__ float red[66];
@@ -308,6 +309,8 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
     float* part = trig + rot;              // with head_norm: the sum of squares of every four neighbouring values
     float* hinv = part + (NQ + NK) / 4;    // ... and 1 / root mean square of every head
     const int pos = live ? positions[t] : 0;
+    // a query's temperature: it grows with the logarithm of how many whole stretches of qt_every positions lie before it
+    const float q_temp = qt_every > 0 ? 1.f + qt_coef * logf((float)((pos + 1) / qt_every) + 1.f) : 1.f;
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
     int page = 0;
     if (live && store_kv) {
@@ -349,7 +352,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
             }
         }
         float inv_q = 1.f, inv_k = 1.f;
-        if (q_norm || k_norm) {  // (its barriers also publish vals and trig)
+        if (!head_norm && (q_norm || k_norm)) {  // (its barriers also publish vals and trig)
             float both[2] = {sq, sk};
             block_sums<2>(both, red);
             if (q_norm) inv_q = rsqrtf(both[0] / (float)NQ + eps);
@@ -367,6 +370,23 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
                 hinv[h] = rsqrtf(ss / (float)d + eps);
             }
             __syncthreads();
+        } else if (head_norm && (q_norm || k_norm || interleaved)) {
+            // a warp a head, the norm BEFORE the rotation (a weight of d elements that all heads share does not commute
+            // with it): the head's sum of squares over the lanes in a fixed order, the division, the weight; what follows
+            // rotates and writes the heads out
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+            for (int h = warp; h < nq + nkv; h += nwarps) {
+                float* hv = vals + h * d;
+                const TP* nw = h < nq ? q_norm : k_norm;
+                float ss = 0.f;
+                for (int i = lane; i < d; i += 32) ss = fmaf(hv[i], hv[i], ss);
+                ss = warp_sum(ss);
+                const float inv = rsqrtf(ss / (float)d + eps);
+                __syncwarp();
+                for (int i = lane; i < d; i += 32) hv[i] = hv[i] * inv * (nw ? to_float(nw[i]) : 1.f);
+            }
+            __syncthreads();
+            q_norm = k_norm = nullptr;
         } else if (head_norm) {
             // a warp a head: the rotation in place, the head's sum of squares over the lanes in a fixed order, the division;
             // what follows writes the heads out as they are
@@ -399,16 +419,18 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
         if (vec4) {
             // q and k: one item per (head, four dims); an item of the rotated part's first half also makes its partner, so a
             // head has dp / 4 - half / 4 items.  Head and item of a thread move on by additions (no division in the loop).
-            const int upd = dp / 4, hq = half / 4, uh = upd - hq;
+            const int halfv = interleaved ? 0 : half;  // (interleaved pairs lie inside an item: no partner item)
+            const int upd = dp / 4, hq = halfv / 4, uh = upd - hq;
             {
                 int h = threadIdx.x / uh, u = threadIdx.x % uh;
                 const int dh = blockDim.x / uh, du = blockDim.x % uh;
                 while (h < heads) {
-                    const int i = u < hq ? 4 * u : 4 * u + half;
+                    const int i = u < hq ? 4 * u : 4 * u + halfv;
                     const bool is_q = h < nq;
                     T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
-                    const int base = h * d, nb = is_q ? base : base - NQ;  // k heads follow the q heads in vals
-                    const float inv = head_inv ? hinv[h] : (is_q ? inv_q : inv_k);
+                    // k heads follow the q heads in vals; a weight beside a norm per head has d elements, for every head
+                    const int base = h * d, nb = head_inv ? 0 : (is_q ? base : base - NQ);
+                    const float inv = (head_inv ? hinv[h] : (is_q ? inv_q : inv_k)) * (is_q ? q_temp : 1.f);
                     const TP* nw = is_q ? q_norm : k_norm;
                     auto normed4 = [&](int j, float (&o)[4]) {
                         float wv[4] = {1.f, 1.f, 1.f, 1.f};
@@ -429,6 +451,11 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
                         store4(dst + i + half, hi);
                     } else if (i < d) {
                         normed4(i, r);
+                        if (interleaved && i < rot) {  // dimension 2j with 2j + 1, both inside this item
+                            const float a0 = r[0], b0 = r[1], a1 = r[2], b1 = r[3];
+                            rotate_pair(a0, b0, trig[i / 2], trig[half + i / 2], r[0], r[1]);
+                            rotate_pair(a1, b1, trig[i / 2 + 1], trig[half + i / 2 + 1], r[2], r[3]);
+                        }
                     }
                     store4(dst + i, r);
                     u += du;
@@ -477,7 +504,12 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
                 const TP* nw = is_q ? q_norm : k_norm;
                 const int nb = is_q ? base : base - NQ;
                 auto normed = [&](int j) { return vals[base + j] * inv * (nw ? to_float(nw[nb + j]) : 1.f); };
-                if (i < rot) {
+                if (i < rot && interleaved) {
+                    const int f = i >> 1;
+                    float lo, hi;
+                    rotate_pair(normed(i & ~1), normed(i | 1), trig[f], trig[half + f], lo, hi);
+                    r = i & 1 ? hi : lo;
+                } else if (i < rot) {
                     const int f = i < half ? i : i - half;
                     float lo, hi;
                     rotate_pair(normed(f), normed(f + half), trig[f], trig[half + f], lo, hi);
@@ -485,6 +517,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, long long qkv_stride, const TP* __
                 } else {
                     r = normed(i);
                 }
+                if (is_q) r *= q_temp;
             }
             dst[i] = from_float<T>(r);
         }
@@ -508,9 +541,9 @@ extern "C" int qkv_prepare(const void* qkv, long long qkv_stride, int dtype, con
                            const int* positions, const int* token_entry, const int* meta, int group, const float* inv_freq,
                            int rot, const void* v_first, const float* v_lambda, void* v_out, void* q_out, void* cache, int T,
                            int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages, int store_kv, int head_norm,
-                           int* status, cudaStream_t stream) {
+                           int interleaved, float qt_coef, int qt_every, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (head_norm && (q_norm || k_norm)) return (int)cudaErrorInvalidValue;
+    if (interleaved && rot % 2) return (int)cudaErrorInvalidValue;
     const size_t smem = ((size_t)(nq + nkv) * d + rot + (head_norm ? (size_t)(nq + nkv) * (d / 4 + 1) : 0)) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     // Few tokens: 256 threads a block, the shortest path through a token.  Many: 128, so that more blocks, each at another
@@ -518,7 +551,7 @@ extern "C" int qkv_prepare(const void* qkv, long long qkv_stride, int dtype, con
     const int threads = (nq + nkv) * d >= 1024 && T < 512 ? 256 : 128;
     const uintptr_t all = (uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)v_first |
                           (uintptr_t)v_out | (uintptr_t)q_out | (uintptr_t)cache;
-    const int vec4 = d % 4 == 0 && dv % 4 == 0 && dp % 4 == 0 && rot % 8 == 0 && qkv_stride % 4 == 0 && (all & 15) == 0;
+    const int vec4 = d % 4 == 0 && dv % 4 == 0 && dp % 4 == 0 && rot % (interleaved ? 4 : 8) == 0 && qkv_stride % 4 == 0 && (all & 15) == 0;
     cudaError_t e;
     static size_t configured[3] = {0, 0, 0};  // the attribute only ever grows (and is not set inside a capture again)
 #define PREP_CASE(TT, TP, which) \
@@ -531,7 +564,7 @@ extern "C" int qkv_prepare(const void* qkv, long long qkv_stride, int dtype, con
         return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT, TP>, T, threads, smem, stream, \
                                       (const TT*)qkv, qkv_stride, (const TP*)bias, (const TP*)q_norm, (const TP*)k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, \
                                       (const TT*)v_first, v_lambda, (TT*)v_out, (TT*)q_out, (TT*)cache, nq, nkv, d, dv, dp, \
-                                      page_size, num_pages, store_kv, vec4, head_norm, status); \
+                                      page_size, num_pages, store_kv, vec4, head_norm, interleaved, qt_coef, qt_every, status); \
     } while (0)
     if (dtype == DT_F32 && param_dtype != DT_F32) return (int)cudaErrorInvalidValue;
     if (dtype == DT_F32) PREP_CASE(float, float, 0);

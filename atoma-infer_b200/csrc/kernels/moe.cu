@@ -11,7 +11,7 @@
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
-                 const int* __restrict__ meta, int H, int E, int top) {
+                 const int* __restrict__ meta, int H, int E, int top, const float* __restrict__ bias, int over_chosen) {
     extern __shared__ float z[];  // E logits, then E scores that selection consumes
     pdl_wait();
     pdl_launch_dependents();
@@ -37,11 +37,29 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w, int* __re
             for (int k = lane; k < H; k += 32) acc = fmaf(to_float(x[k]), we[k], acc);
         }
         acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc;
+        if (lane == 0) z[e] = acc + (bias ? bias[e] : 0.f);
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
     float* s = z + E;
+    if (over_chosen) {
+        // the largest logits choose (ties to the lower index); the weights are the softmax over the chosen logits alone
+        float first = 0.f, sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = 0;
+            float bv = -INFINITY;
+            for (int e = 0; e < E; ++e)
+                if (z[e] > bv) { bv = z[e]; best = e; }
+            if (k == 0) first = bv;
+            const float w_k = expf(bv - first);
+            ids[(size_t)t * top + k] = best;
+            wts[(size_t)t * top + k] = w_k;
+            sum += w_k;
+            z[best] = -INFINITY;
+        }
+        for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] = wts[(size_t)t * top + k] / sum;
+        return;
+    }
     float mx = -INFINITY, sum = 0.f;
     for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[e]);
     for (int e = 0; e < E; ++e) { s[e] = expf(z[e] - mx); sum += s[e]; }
@@ -60,16 +78,26 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w, int* __re
     for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] = wts[(size_t)t * top + k] / (chosen + 1e-20f);
 }
 
+extern "C" int moe_route_biased(const void* h, int dtype, const float* w, const float* bias, int over_chosen, int* ids, float* wts,
+                                const int* meta, int T, int H, int E, int top, cudaStream_t stream);
+
 extern "C" int moe_route(const void* h, int dtype, const float* w, int* ids, float* wts, const int* meta, int T, int H, int E,
                          int top, cudaStream_t stream) {
+    return moe_route_biased(h, dtype, w, nullptr, 0, ids, wts, meta, T, H, E, top, stream);
+}
+
+// bias (float32 [E], or null) is added to the logits.  over_chosen: the weights are the softmax over the chosen experts'
+// logits alone (else: the softmax over all experts, the chosen scores divided by their sum).
+extern "C" int moe_route_biased(const void* h, int dtype, const float* w, const float* bias, int over_chosen, int* ids, float* wts,
+                                const int* meta, int T, int H, int E, int top, cudaStream_t stream) {
     if (T <= 0) return 0;
     const size_t smem = (size_t)2 * E * sizeof(float);
     if (smem > 48 * 1024 || top > E) return (int)cudaErrorInvalidValue;
     if (dtype == DT_F32)
         return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, moe_route_kernel<float>, T, 256, smem, stream, (const float*)h, w, ids, wts,
-                                      meta, H, E, top);
+                                      meta, H, E, top, bias, over_chosen);
     return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, moe_route_kernel<__nv_bfloat16>, T, 256, smem, stream,
-                                  (const __nv_bfloat16*)h, w, ids, wts, meta, H, E, top);
+                                  (const __nv_bfloat16*)h, w, ids, wts, meta, H, E, top, bias, over_chosen);
 }
 
 // ----------------------------------------------------------------------------- pairs sorted by expert

@@ -55,8 +55,10 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
                 long long slot_stride, float* __restrict__ o, const int* __restrict__ meta,
                 const int* __restrict__ cu_tokens, const int* __restrict__ slots, int heads, int P, int N, int R, int PB,
                 int col_blocks, int pass, int chunk_len, int max_chunks, float* __restrict__ scratch,
-                float* __restrict__ decay, int vec) {
+                float* __restrict__ decay, int vec, int mode) {
     extern __shared__ __align__(16) float sm[];
+    // mode bit 0: no logits; every row of head h decays by the constant z_bias[h].  bit 1: q, k and v pass through SiLU.
+    const bool fixed = mode & 1, act = mode & 2;
     const int SL = R > 1 ? NPT + 4 : NPT, NL = R * NPT, NP = R * SL;  // row n lies at (n / NPT) * SL + n % NPT
     float* qs = sm;                     // [REC_TT][NP]
     float* ks = qs + REC_TT * NP;       // [REC_TT][NP]
@@ -114,7 +116,7 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
                         const size_t t = (size_t)(tb + tt), hn = (size_t)h * N + n;
                         rq[u] = *reinterpret_cast<const Raw4<T>*>(q + t * q_stride + hn);
                         rk[u] = *reinterpret_cast<const Raw4<T>*>(k + t * k_stride + hn);
-                        rz[u] = *reinterpret_cast<const float4*>(z + t * z_stride + hn);
+                        if (!fixed) rz[u] = *reinterpret_cast<const float4*>(z + t * z_stride + hn);
                     }
                 }
 #pragma unroll
@@ -123,12 +125,22 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
                     float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f), k4 = q4, a4 = make_float4(1.f, 1.f, 1.f, 1.f);
                     if (in[u]) {
                         // (the bias is the same for every token: it stays in the first-level cache)
+                        float qv[4], kv[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            qv[j] = to_float(rq[u].x[j]), kv[j] = to_float(rk[u].x[j]);
+                            if (act) qv[j] = silu_f(qv[j]), kv[j] = silu_f(kv[j]);
+                        }
+                        q4 = make_float4(qv[0] * q_scale, qv[1] * q_scale, qv[2] * q_scale, qv[3] * q_scale);
+                        k4 = make_float4(kv[0], kv[1], kv[2], kv[3]);
+                        if (fixed) {
+                            const float a = z_bias[h];
+                            a4 = make_float4(a, a, a, a);
+                        } else {
                         const float4 rb = z_bias ? *reinterpret_cast<const float4*>(z_bias + hn4[u]) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        q4 = make_float4(to_float(rq[u].x[0]) * q_scale, to_float(rq[u].x[1]) * q_scale, to_float(rq[u].x[2]) * q_scale,
-                                         to_float(rq[u].x[3]) * q_scale);
-                        k4 = make_float4(to_float(rk[u].x[0]), to_float(rk[u].x[1]), to_float(rk[u].x[2]), to_float(rk[u].x[3]));
                         a4 = make_float4(expf(-softplus_f(-(rz[u].x + rb.x)) * inv_tau), expf(-softplus_f(-(rz[u].y + rb.y)) * inv_tau),
                                          expf(-softplus_f(-(rz[u].z + rb.z)) * inv_tau), expf(-softplus_f(-(rz[u].w + rb.w)) * inv_tau));
+                        }
                     }
                     *reinterpret_cast<float4*>(qs + at[u]) = q4;
                     *reinterpret_cast<float4*>(ks + at[u]) = k4;
@@ -149,9 +161,12 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
                     if (at[u] < 0) continue;
-                    *reinterpret_cast<float4*>(vs + at[u]) =
-                        in[u] ? make_float4(to_float(rv[u].x[0]), to_float(rv[u].x[1]), to_float(rv[u].x[2]), to_float(rv[u].x[3]))
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
+                    float vv4[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (in[u]) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) vv4[j] = act ? silu_f(to_float(rv[u].x[j])) : to_float(rv[u].x[j]);
+                    }
+                    *reinterpret_cast<float4*>(vs + at[u]) = make_float4(vv4[0], vv4[1], vv4[2], vv4[3]);
                 }
             }
         } else {
@@ -160,11 +175,17 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
             const size_t t = (size_t)(tb + tt);
             float qv = 0.f, kv = 0.f, av = 1.f;
             if (n < N) {
-                qv = to_float(q[t * q_stride + (size_t)h * N + n]) * q_scale;
+                qv = to_float(q[t * q_stride + (size_t)h * N + n]);
                 kv = to_float(k[t * k_stride + (size_t)h * N + n]);
-                // sigmoid(x)^(1/tau) = exp(-softplus(-x) / tau)
-                const float x = z[t * z_stride + (size_t)h * N + n] + (z_bias ? z_bias[(size_t)h * N + n] : 0.f);
-                av = expf(-softplus_f(-x) * inv_tau);
+                if (act) qv = silu_f(qv), kv = silu_f(kv);
+                qv *= q_scale;
+                if (fixed) {
+                    av = z_bias[h];
+                } else {
+                    // sigmoid(x)^(1/tau) = exp(-softplus(-x) / tau)
+                    const float x = z[t * z_stride + (size_t)h * N + n] + (z_bias ? z_bias[(size_t)h * N + n] : 0.f);
+                    av = expf(-softplus_f(-x) * inv_tau);
+                }
             }
             qs[at] = qv;
             ks[at] = kv;
@@ -172,7 +193,8 @@ gla_scan_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict
         }
         for (int idx = tid; idx < nt * PB; idx += blockDim.x) {
             const int tt = idx / PB, pc = cb * PB + idx % PB;
-            vs[idx] = pc < P ? to_float(v[(size_t)(tb + tt) * v_stride + (size_t)h * P + pc]) : 0.f;
+            const float x = pc < P ? to_float(v[(size_t)(tb + tt) * v_stride + (size_t)h * P + pc]) : 0.f;
+            vs[idx] = act ? silu_f(x) : x;
         }
         }
         __syncthreads();
@@ -304,11 +326,29 @@ extern "C" size_t gla_scan_scratch_floats(int S, int heads, int N, int P, int ma
     return (size_t)S * max_chunks * heads * ((size_t)N * P + N);
 }
 
+extern "C" int gla_scan_mode(const void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
+                             int dtype, const float* z, long long z_stride, const float* z_bias, float tau, float q_scale,
+                             float* state, long long slot_stride, float* o, const int* meta, const int* cu_tokens, const int* slots,
+                             int S, int heads, int N, int P, int chunk_len, int max_chunks, float* scratch, int mode,
+                             cudaStream_t stream);
+
 extern "C" int gla_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
                         int dtype, const float* z, long long z_stride, const float* z_bias, float tau, float q_scale,
                         float* state, long long slot_stride, float* o, const int* meta, const int* cu_tokens, const int* slots,
                         int S, int heads, int N, int P, int chunk_len, int max_chunks, float* scratch, cudaStream_t stream) {
+    return gla_scan_mode(q, q_stride, k, k_stride, v, v_stride, dtype, z, z_stride, z_bias, tau, q_scale, state, slot_stride, o, meta,
+                         cu_tokens, slots, S, heads, N, P, chunk_len, max_chunks, scratch, 0, stream);
+}
+
+// mode bit 0: the decay is a constant per head, z_bias[h] (float32 [heads]; z is not read); bit 1: q, k and v pass through
+// SiLU as they are loaded.
+extern "C" int gla_scan_mode(const void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
+                             int dtype, const float* z, long long z_stride, const float* z_bias, float tau, float q_scale,
+                             float* state, long long slot_stride, float* o, const int* meta, const int* cu_tokens, const int* slots,
+                             int S, int heads, int N, int P, int chunk_len, int max_chunks, float* scratch, int mode,
+                             cudaStream_t stream) {
     if (S <= 0) return 0;
+    if ((mode & 1) ? !z_bias : !z) return (int)cudaErrorInvalidValue;
     int NPT = 0, R = 0, PB = 0;
     if (tau <= 0.f || !rec_geometry(N, P, &NPT, &R, &PB)) return (int)cudaErrorInvalidValue;
     const bool chunked = chunk_len > 0 && max_chunks > 1 && scratch;
@@ -323,7 +363,7 @@ extern "C" int gla_scan(const void* q, long long q_stride, const void* k, long l
     const uintptr_t esz = dtype == DT_F32 ? 4 : 2;
     const int vec = N % 4 == 0 && P % 4 == 0 && PB % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 &&
                     z_stride % 4 == 0 && ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % (4 * esz) == 0 &&
-                    ((uintptr_t)z | (uintptr_t)z_bias) % 16 == 0;
+                    ((mode & 1) || ((uintptr_t)z | (uintptr_t)z_bias) % 16 == 0);
     const int col_blocks = (P + PB - 1) / PB, threads = ((PB / CPT * R + 31) / 32) * 32;
     const size_t smem = (size_t)(3 * REC_TT * R * (R > 1 ? NPT + 4 : NPT) + REC_TT * PB) * sizeof(float);
     if (smem > 96 * 1024) return (int)cudaErrorInvalidValue;
@@ -340,7 +380,7 @@ extern "C" int gla_scan(const void* q, long long q_stride, const void* k, long l
         err = (int)launch_kernel(gla_scan_kernel<TT, K, W, C>, dim3(heads * col_blocks, S, chunks), threads, smem, stream, (const TT*)q, q_stride, \
                                  (const TT*)k, k_stride, (const TT*)v, v_stride, z, z_stride, z_bias, inv_tau, q_scale, state, \
                                  slot_stride, o, meta, cu_tokens, slots, heads, P, N, R, PB, col_blocks, pass, chunk_len,     \
-                                 max_chunks, scratch, decay, vec);                                                         \
+                                 max_chunks, scratch, decay, vec, mode);                                                   \
     }
 #define GLA_CASE(TT, K, W, pass, chunks)                                                                                    \
     case K:                                                                                                                \

@@ -30,7 +30,7 @@ GEMM_SOURCES = ["kernels/gemm_tcgen05.cu"]
 ATTENTION_TC_SOURCES = ["kernels/attention_tcgen05.cu"]
 DECODE_STACK_SOURCES = ["kernels/decode_stack.cu"]
 # parallel blocks, state-space mixers, latent attention, routed experts: built when a model first uses one of them
-MIXER_SOURCES = ["kernels/stream_ops.cu", "kernels/ssm.cu", "kernels/latent.cu", "kernels/moe.cu"]
+MIXER_SOURCES = ["kernels/stream_ops.cu", "kernels/ssm.cu", "kernels/latent.cu", "kernels/moe.cu", "kernels/gated_stream.cu"]
 # recurrences whose decay differs from row to row (gated linear attention, the selective scan): built at first use too
 RECURRENT_SOURCES = ["kernels/recurrent.cu"]
 ATTENTION_TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prefill attention
@@ -389,15 +389,21 @@ class CudaOps:
 
     def qkv_prepare(self, qkv, ctx, cache_layer, group: int, q_out, *, nq: int, nkv: int, d: int, dv: int, dp: int,
                     page_size: int, num_pages: int, store_kv: bool, bias=None, q_norm=None, k_norm=None, eps: float = 0.0,
-                    inv_freq=None, rot: int = 0, v_first=None, v_lambda=None, v_out=None, head_norm: bool = False):
+                    inv_freq=None, rot: int = 0, v_first=None, v_lambda=None, v_out=None, head_norm: bool = False,
+                    interleaved: bool = False, q_temp=None):
         """Rows [q | k | v] of the fused projection become attention's inputs: biases, root-mean-square norms over
         the whole q and the whole k part (weights ``q_norm`` / ``k_norm``), rotation of the first ``rot`` dims of
         every head, with ``head_norm`` every q and k head divided by its own root mean square (``eps``) after the rotation,
         v <- (1 - lambda) v + lambda v_first; q to ``q_out`` [T, nq * dp], k and v to the pages as heads of
         dp elements (zeros behind d and dv).  ``v_out``: the values (biases added, unmixed) for later layers.
-        ``bias``, ``q_norm`` and ``k_norm`` share one type, float32 or (beside bfloat16 rows) bfloat16."""
-        if head_norm and (q_norm is not None or k_norm is not None):
-            raise KernelError("attention rows are normed over the whole projection or head by head, not both")
+        ``bias``, ``q_norm`` and ``k_norm`` share one type, float32 or (beside bfloat16 rows) bfloat16.
+        With ``head_norm`` AND weights, the weights have ``d`` elements, shared by all heads, and the norm comes before the
+        rotation.  ``interleaved``: the rotation pairs dimension 2i with 2i + 1 (else i with i + rot / 2).  ``q_temp`` =
+        (coef, every): the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)."""
+        if head_norm and (q_norm is not None or k_norm is not None) and (q_norm is None or k_norm is None
+                                                                           or q_norm.numel() != d or k_norm.numel() != d):
+            raise KernelError("weights beside a norm per head have the head's size, for queries and for keys")
+        qt_coef, qt_every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
         params = [t for t in (bias, q_norm, k_norm) if t is not None]
         if len({t.dtype for t in params}) > 1:
             raise KernelError("biases and norm weights of the attention rows must share one type")
@@ -407,7 +413,8 @@ class CudaOps:
                                          _p(ctx.positions), _p(ctx.token_entry), _p(ctx.meta), max(group, 0), _p(inv_freq),
                                          int(rot) if inv_freq is not None else 0, _p(v_first), _p(v_lambda), _p(v_out),
                                          _p(q_out), _p(cache_layer), ctx.T, nq, nkv, d, dv, dp, page_size, num_pages,
-                                         int(store_kv), int(head_norm), _p(self.status), self._stream()), "qkv_prepare")
+                                         int(store_kv), int(head_norm), int(interleaved), ctypes.c_float(qt_coef), qt_every,
+                                         _p(self.status), self._stream()), "qkv_prepare")
 
     def narrow(self, x, dtype):
         """Float32 rows in the compute type (rounded once); the same tensor if it has that type already."""
@@ -436,7 +443,8 @@ class CudaOps:
                 and q_stride % 8 == 0)
 
     def attention(self, q, q_stride: int, cache_layer, ctx, group: int, out, nq: int, nkv: int, d: int,
-                  page_size: int, num_pages: int, window: int, scale: float, rope=None, chunk: int = 0, sink: bool = False):
+                  page_size: int, num_pages: int, window: int, scale: float, rope=None, chunk: int = 0, sink: bool = False,
+                  keep_first: int = 0, softcap: float = 0.0, slopes=None):
         """Attention of the step's queries over what their requests have cached (the step's own
         keys included).  bfloat16 with a head size in steps of 16 up to 256 runs the tensor-core
         kernels (one library per head size, built at first use); anything else, and all of
@@ -444,8 +452,19 @@ class CudaOps:
         steps on the fast path (see ``fast_attention``); the queries are then still unrotated and the
         kernel rotates them, and writes the new key and value, itself.  ``chunk`` > 0: a query sees only the keys of
         its own chunk of that many positions (chunks counted from position 0 of the request).  ``sink``: the softmax
-        has one more term in its denominator, a key of score 0 without a value."""
+        has one more term in its denominator, a key of score 0 without a value.  ``keep_first`` (beside a window): the
+        first so many keys of a request stay visible behind the window.  ``softcap`` > 0: a score s becomes softcap *
+        tanh(s / softcap).  ``slopes`` (float32, one per query head): slopes[h] * (query position - key position) is
+        taken off the score."""
         T, S = ctx.T, ctx.S
+        if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != nq or not slopes.is_contiguous()):
+            raise KernelError("distance slopes are one contiguous float32 number per query head")
+        if (keep_first and window) or softcap or slopes is not None:
+            if rope is not None:
+                raise KernelError("the fused rotation does not go with kept first tokens, a score cap or distance slopes")
+            if self._attention_scores(q, q_stride, cache_layer, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale,
+                                      chunk, sink, int(keep_first) if window else 0, float(softcap), slopes):
+                return
         # a learned sink: one float32 score per query head (a tensor) instead of the score 0 (True)
         sinks = sink if torch.is_tensor(sink) else None
         sink = sinks is not None or bool(sink)
@@ -515,6 +534,86 @@ class CudaOps:
                                                 _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
                                                 num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
                                                 ctypes.c_float(scale), _p(self.status), self._stream()), "attn_generic")
+
+    def _attention_scores(self, q, q_stride, cache_layer, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale,
+                          chunk, sink, keep_first, softcap, slopes) -> bool:
+        """Attention whose scores are capped, biased by distance, or masked by a window that keeps the first tokens: on the
+        plain kernel (both number formats)."""
+        sinks = sink if torch.is_tensor(sink) else None
+        if d > 512:
+            raise KernelError(f"head size {d} is not supported (at most 512)")
+        self._check(self.lib.attn_generic_scores(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
+                                                 _p(ctx.token_entry), _p(ctx.positions), _p(out), ctx.T, nq, nkv, d, page_size,
+                                                 num_pages, window, int(chunk), int(sinks is not None or bool(sink)), _p(sinks),
+                                                 ctypes.c_float(scale), keep_first, ctypes.c_float(softcap), _p(slopes),
+                                                 _p(self.status), self._stream()), "attn_generic")
+        return True
+
+    # ------------------------------------------------------------------ blocks that norm a sublayer's result and gate it
+    def norm_shift(self, resid, w, eps: float, ctx, *, shift=None, state=None, h=None, hs=None, last=None):
+        """h[t] = rmsnorm(resid[t]) * w and hs[t] = h[t] + (h[t - 1] - h[t]) * shift, h[t - 1] being the normed row of the
+        token before in the same request: of this step, or the row kept in ``state`` (float32 [slots, H] with a slot
+        stride), or zeros at position 0.  ``last`` (float32 [S, H]) receives every entry's last normed row, which
+        ``gated_norm_add`` moves into the state once nothing reads the old one any more.  Without ``shift`` hs = h."""
+        H = resid.shape[1]
+        outs = [t for t in (h, hs) if t is not None]
+        if not outs or len({t.dtype for t in outs}) > 1:
+            raise KernelError("norm_shift writes h, hs or both, of one type")
+        stride = ctypes.c_longlong(state.stride(0)) if state is not None else ctypes.c_longlong(0)
+        if state is not None and (state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] != H):
+            raise KernelError("the kept row is float32 [slots, H] with contiguous rows")
+        self._check(self._mixers().norm_shift(_p(resid), _p(w), ctypes.c_float(eps), _p(shift), _p(state), stride, _p(h), _p(hs),
+                                              _code(outs[0]), _p(last), _p(ctx.meta), _p(ctx.positions), _p(ctx.token_entry),
+                                              _p(ctx.cu_tokens), _p(ctx.state_slots), ctx.T, H, self._stream()), "norm_shift")
+
+    def gated_norm_add(self, resid, pending, gate, gate_bias, w, eps: float, ctx, *, next_norm=None, keep=None):
+        """resid[t] += rmsnorm(y[t] * sigmoid(gate[t] + gate_bias)) * w with y = mult * (f0 t0 + f1 t1 + ...) + vector, the
+        terms, weights, factor and vector of ``pending`` (a ``PendingSum``; up to four terms of one type).  ``gate``: the
+        gate's logits [T, H] (float32, or the terms' type), ``gate_bias`` float32 [H] or None.  ``next_norm`` = (w2, eps2,
+        out): also out[t] = rmsnorm(resid[t]) * w2, the next sublayer's input.  ``keep`` = (last, state): every entry's row
+        of ``last`` moves into its slot of ``state`` (see ``norm_shift``)."""
+        H = resid.shape[1]
+        terms = list(pending.terms)
+        if not 0 < len(terms) <= 4 or len({t.dtype for t in terms}) > 1:
+            raise KernelError("a gated sum has one to four terms, of one type")
+        if pending.rows is not None:
+            raise KernelError("a gated sum has terms, weights, a factor and a vector only")
+        ptrs = (ctypes.c_void_p * 4)(*[t.data_ptr() for t in terms])
+        facs = (ctypes.c_float * 4)(*pending.weights())
+        w2, eps2, out = next_norm if next_norm is not None else (None, 0.0, None)
+        last, state = keep if keep is not None else (None, None)
+        stride = ctypes.c_longlong(state.stride(0)) if state is not None else ctypes.c_longlong(0)
+        self._check(self._mixers().gated_norm_add(_p(resid), len(terms), ptrs, facs, _code(terms[0]), ctypes.c_float(pending.mult),
+                                                  _p(pending.vector), _p(gate), _code(gate), _p(gate_bias), _p(w), ctypes.c_float(eps),
+                                                  _p(w2), ctypes.c_float(eps2), _p(out), _code(out) if out is not None else _code(terms[0]),
+                                                  _p(last), _p(state), stride, _p(ctx.meta), _p(ctx.token_entry), _p(ctx.cu_tokens),
+                                                  _p(ctx.state_slots), ctx.T, H, self._stream()), "gated_norm_add")
+
+    def clamped_glu(self, gu, out, limit: float, alpha: float, meta):
+        """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); ``gu`` [T, 2F], the
+        gate's columns first."""
+        self._check(self._mixers().clamped_glu(_p(gu), _p(out), _code(gu), _p(meta), gu.shape[0], out.shape[1], ctypes.c_float(limit),
+                                               ctypes.c_float(alpha), self._stream()), "clamped_glu")
+
+    def head_gate(self, y, gate, meta):
+        """y[t, h, :] *= sigmoid(gate[t, h]) in place: ``y`` [T, heads, n] with a contiguous last axis, ``gate`` [T, heads] a
+        slice of wider rows."""
+        T, heads, n = y.shape
+        yp, yt, yh = self._heads(y, "head_gate")
+        gp, gs = self._rows(gate, "head_gate")
+        self._check(self._mixers().head_gate(yp, yt, yh, gp, gs, _code(y), _p(meta), T, heads, n, self._stream()), "head_gate")
+
+    def row_norm_gate(self, o, gate, w, eps: float, out, meta, kind: str = "sigmoid"):
+        """out[t] = o[t] / sqrt(mean(o[t]^2) + eps) * w * gate_fn(gate[t]): ``o`` float32 [T, n], ``gate`` a slice of wider rows,
+        ``w`` float32 [n]; ``kind``: "sigmoid" or "silu"."""
+        gp, gs = self._rows(gate, "row_norm_gate")
+        self._check(self._mixers().row_norm_gate(_p(o), gp, _code(gate), gs, _p(w), ctypes.c_float(eps), _p(out), _p(meta), o.shape[0],
+                                                 o.shape[1], {"sigmoid": 0, "silu": 1}[kind], self._stream()), "row_norm_gate")
+
+    def scale_softcap(self, logits, scale: float, cap: float, meta):
+        """logits <- cap * tanh(logits * scale / cap) in place (cap 0: logits * scale); float32 [rows, n]."""
+        self._check(self._mixers().scale_softcap(_p(logits), _p(meta), logits.shape[0], logits.shape[1], ctypes.c_float(scale),
+                                                 ctypes.c_float(cap), self._stream()), "scale_softcap")
 
     # ------------------------------------------------------------------ parallel blocks, state-space mixers, latent attention, experts
     def _mixers(self):
@@ -698,22 +797,33 @@ class CudaOps:
             raise KernelError(f"{what}: the state is float32 [slots, {', '.join(map(str, shape))}] with contiguous slots")
         return ctypes.c_longlong(state.stride(0))
 
-    def gla_scan(self, q, k, v, z, z_bias, tau: float, q_scale: float, state, ctx, o, *, heads: int, dim: int, vdim: int):
+    def gla_scan(self, q, k, v, z, z_bias, tau: float, q_scale: float, state, ctx, o, *, heads: int, dim: int, vdim: int,
+                 head_decay=None, silu: bool = False):
         """Gated linear attention of every entry's tokens: per head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_scale
         q_t), a_t = sigmoid(z_t + z_bias)^(1 / tau).  q, k [T, heads * dim] and v [T, heads * vdim] are slices of wider rows,
         ``z`` float32 [T, heads * dim], ``state`` float32 [slots, heads, dim, vdim] (read and updated), ``o`` float32
-        [T, heads * vdim]."""
+        [T, heads * vdim].  ``head_decay`` (float32 [heads]) instead of ``z``: every row of head h decays by the constant
+        head_decay[h].  ``silu``: q, k and v pass through SiLU first."""
         lib = self._recurrent()
         slot_stride = self._slot_state(state, (heads, dim, vdim), "gla_scan")
-        if z.dtype != torch.float32 or o.dtype != torch.float32 or not o.is_contiguous():
-            raise KernelError("gla_scan: decay logits and outputs are float32")
-        (qp, qs), (kp, ks), (vp, vs), (zp, zs) = (self._rows(t, "gla_scan") for t in (q, k, v, z))
+        if o.dtype != torch.float32 or not o.is_contiguous():
+            raise KernelError("gla_scan: outputs are float32")
+        (qp, qs), (kp, ks), (vp, vs) = (self._rows(t, "gla_scan") for t in (q, k, v))
+        if head_decay is not None:
+            if z is not None or head_decay.dtype != torch.float32 or head_decay.numel() != heads:
+                raise KernelError("gla_scan: a constant decay is one float32 number per head, given instead of logits")
+            zp, zs, z_bias, tau = None, ctypes.c_longlong(0), head_decay, 1.0
+        else:
+            if z.dtype != torch.float32:
+                raise KernelError("gla_scan: decay logits are float32")
+            zp, zs = self._rows(z, "gla_scan")
+        mode = (1 if head_decay is not None else 0) | (2 if silu else 0)
         chunk, chunks = self._scan_chunks(ctx)
         scratch = (torch.empty(lib.gla_scan_scratch_floats(ctx.S, heads, dim, vdim, chunks), dtype=torch.float32, device=o.device)
                    if chunk else None)
-        self._check(lib.gla_scan(qp, qs, kp, ks, vp, vs, _code(q), zp, zs, _p(z_bias), ctypes.c_float(tau), ctypes.c_float(q_scale),
-                                 _p(state), slot_stride, _p(o), _p(ctx.meta), _p(ctx.cu_tokens), _p(ctx.state_slots), ctx.S,
-                                 heads, dim, vdim, chunk, chunks, _p(scratch), self._stream()), "gla_scan")
+        self._check(lib.gla_scan_mode(qp, qs, kp, ks, vp, vs, _code(q), zp, zs, _p(z_bias), ctypes.c_float(tau), ctypes.c_float(q_scale),
+                                      _p(state), slot_stride, _p(o), _p(ctx.meta), _p(ctx.cu_tokens), _p(ctx.state_slots), ctx.S,
+                                      heads, dim, vdim, chunk, chunks, _p(scratch), mode, self._stream()), "gla_scan")
         if chunk:
             self.launches += 2
 
@@ -743,12 +853,13 @@ class CudaOps:
         if chunk:
             self.launches += 2
 
-    def moe_route(self, h, w_router, ids, wts, meta):
-        """Per token: float32 logits w_router h, softmax over all experts, the ids.shape[1] largest scores (ties to the
-        lower index) into ``ids`` (int32) and those scores divided by their sum (+ 1e-20) into ``wts`` (float32)."""
+    def moe_route(self, h, w_router, ids, wts, meta, bias=None, over_chosen: bool = False):
+        """Per token: float32 logits w_router h (+ ``bias``, float32 [experts]), softmax over all experts, the ids.shape[1]
+        largest scores (ties to the lower index) into ``ids`` (int32) and those scores divided by their sum (+ 1e-20) into
+        ``wts`` (float32).  ``over_chosen``: the weights are the softmax over the chosen experts' logits alone."""
         E, H = w_router.shape
-        self._check(self._mixers().moe_route(_p(h), _code(h), _p(w_router), _p(ids), _p(wts), _p(meta), h.shape[0], H, E,
-                                             ids.shape[1], self._stream()), "moe_route")
+        self._check(self._mixers().moe_route_biased(_p(h), _code(h), _p(w_router), _p(bias), int(over_chosen), _p(ids), _p(wts),
+                                                    _p(meta), h.shape[0], H, E, ids.shape[1], self._stream()), "moe_route")
 
     MOE_PAIR_ROWS = 64       # up to this many (token, choice) pairs, bfloat16: a pair at a time
     MOE_LIBRARY_ROWS = 256   # from this many pairs on, bfloat16: the library's grouped products

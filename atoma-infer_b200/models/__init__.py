@@ -1,2 +1,2 @@
 """Architectures built from the parts; importing this package registers them."""
-from . import bumolix, dosovik, llama, tutezen  # noqa: F401
+from . import bumolix, dosovik, kulivik, llama, tutezen  # noqa: F401

@@ -219,3 +219,109 @@ class ParallelBlock(Block):
 
 
 register_part("block", "parallel", ParallelBlock)
+
+
+class SandwichBlock(Block):
+    """Norms before AND after each sublayer, a gate on each result, the mixer's input shifted toward the token before:
+
+        h = norm1(x);  x <- x + norm1b(mixer(shift(h)) * sigmoid(R1 h + r1))
+        h2 = norm2(x); x <- x + norm2b(ff(h2) * sigmoid(R2 h2 + r2))
+
+    shift(h)_t = h_t + (h_(t-1) - h_t) * mu per channel, h_(t-1) the normed row of the request's token before (zeros before
+    its first token); a request's last normed row is per-request state (float32, the first share of the block's state,
+    the mixer's share behind it).  The gates read the normed rows as they are, before the shift.  Every sum into the
+    stream is taken by the kernel that norms the gated result, in float32, so the block leaves nothing pending.  A
+    mixer may hand back a ``PendingSum`` (weighted terms, a vector): gate and norm see its float32 value.
+    Parameters: ``norm``, ``mixer``, ``feed_forward`` (None: the mixer alone), ``shift`` (default True), ``names``."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        names = {"norm1": "norm1", "norm1b": "norm1b", "norm2": "norm2", "norm2b": "norm2b", "mixer": "mix", "feed_forward": "mlp",
+                 "shift": ".shift", "gate1": ".rg1", "gate2": ".rg2", "gate_bias": ".b", **(params.get("names") or {})}
+        self.names = names
+        mk = lambda fam, spec, name: part_class(fam, spec["kind"])(spec, f"{prefix}.{name}")  # noqa: E731
+        self.norm1, self.norm1b = mk("norm", params["norm"], names["norm1"]), mk("norm", params["norm"], names["norm1b"])
+        self.mixer = mk("mixer", params["mixer"], names["mixer"])
+        ff = params.get("feed_forward")
+        self.feed_forward = mk("feed_forward", ff, names["feed_forward"]) if ff else None
+        self.norm2 = mk("norm", params["norm"], names["norm2"]) if ff else None
+        self.norm2b = mk("norm", params["norm"], names["norm2b"]) if ff else None
+        self.shift = bool(params.get("shift", True))
+        self.width = self.norm1.size
+
+    def parts(self):
+        return [p for p in (self.norm1, self.norm1b, self.mixer, self.norm2, self.norm2b, self.feed_forward) if p is not None]
+
+    def streamed_weights(self):
+        return ([self.w_gate1] + self.mixer.streamed_weights()
+                + ([self.w_gate2] + self.feed_forward.streamed_weights() if self.feed_forward else []))
+
+    def activation_width(self):
+        return max(p.activation_width() for p in self.parts())
+
+    def declare(self):
+        from ..weights.loader import TensorDecl
+        pre, n, W = self.prefix, self.names, self.width
+        decls = [d for p in self.parts() for d in p.declare()]
+        decls += [TensorDecl(pre + n["gate1"], (W, W)), TensorDecl(pre + n["gate1"] + n["gate_bias"], (W,))]
+        if self.feed_forward is not None:
+            decls += [TensorDecl(pre + n["gate2"], (W, W)), TensorDecl(pre + n["gate2"] + n["gate_bias"], (W,))]
+        if self.shift:
+            decls.append(TensorDecl(pre + n["shift"], (W,)))
+        return decls
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        for p in self.parts():
+            p.bind(tensors, rt)
+        pre, n = self.prefix, self.names
+        f32 = lambda name: tensors[name].to(torch.float32).contiguous()  # noqa: E731  (exact widening)
+        self.w_gate1, self.b_gate1 = tensors[pre + n["gate1"]].contiguous(), f32(pre + n["gate1"] + n["gate_bias"])
+        if self.feed_forward is not None:
+            self.w_gate2, self.b_gate2 = tensors[pre + n["gate2"]].contiguous(), f32(pre + n["gate2"] + n["gate_bias"])
+        self.mu = f32(pre + n["shift"]) if self.shift else None
+
+    def _kept_bytes(self):
+        return -(-self.width * 4 // 16) * 16 if self.shift else 0
+
+    def state_bytes(self):
+        return self._kept_bytes() + self.mixer.state_bytes()
+
+    def forward(self, resid, delta, ctx, cache):
+        from dataclasses import replace
+        from .base import PendingSum
+        ops, dt, dev, T, W = self.rt.ops, self.rt.dtype, resid.device, ctx.T, self.width
+        apply_pending(ops, resid, delta, ctx)  # a block of another kind before this one may have left its addition pending
+        kept, mixer_cache = None, cache
+        if cache.state is not None:
+            nk = self._kept_bytes()
+            if nk:
+                kept = cache.state[:, :W * 4].view(torch.float32)
+            mixer_cache = replace(cache, state=cache.state[:, nk:] if self.mixer.state_bytes() else None)
+        h = torch.empty((T, W), dtype=dt, device=dev)
+        hs, last = h, None
+        if self.shift:
+            hs = torch.empty_like(h)
+            last = torch.empty((ctx.S, W), dtype=torch.float32, device=dev)
+        ops.norm_shift(resid, self.norm1.weight, self.norm1.eps, ctx, shift=self.mu, state=kept, h=h,
+                       hs=hs if self.shift else None, last=last)
+        a = self.mixer.forward(hs, ctx, mixer_cache)
+        if not isinstance(a, PendingSum):
+            a = PendingSum((a,))
+        g = ops.linear(h, self.w_gate1, out_dtype=torch.float32, meta=ctx.meta)
+        keep = (last, kept) if self.shift and kept is not None else None
+        if self.feed_forward is None:
+            ops.gated_norm_add(resid, a, g, self.b_gate1, self.norm1b.weight, self.norm1b.eps, ctx, keep=keep)
+            return None
+        h2 = torch.empty((T, W), dtype=dt, device=dev)
+        ops.gated_norm_add(resid, a, g, self.b_gate1, self.norm1b.weight, self.norm1b.eps, ctx, keep=keep,
+                           next_norm=(self.norm2.weight, self.norm2.eps, h2))
+        f = self.feed_forward.forward(h2, ctx)
+        if not isinstance(f, PendingSum):
+            f = PendingSum((f,))
+        g2 = ops.linear(h2, self.w_gate2, out_dtype=torch.float32, meta=ctx.meta)
+        ops.gated_norm_add(resid, f, g2, self.b_gate2, self.norm2b.weight, self.norm2b.eps, ctx)
+        return None
+
+
+register_part("block", "sandwich", SandwichBlock)

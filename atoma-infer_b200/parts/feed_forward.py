@@ -134,3 +134,46 @@ class DenseActFF(FeedForward):
 
 
 register_part("feed_forward", "dense_act", DenseActFF)
+
+
+class ClampedGLU(FeedForward):
+    """Gated feed-forward with clamped branches: g = min(gate(x), limit), u = clamp(up(x), -limit, limit),
+    down(g * sigmoid(alpha * g) * (u + 1)); no biases.  Gate and up are one stacked matrix.
+
+    Parameters: ``hidden``, ``intermediate``, ``limit``, ``alpha`` (default 1.702), ``names`` (suffixes of gate, up, down;
+    default ``.gate``, ``.up``, ``.down``).
+    """
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.limit, self.alpha = float(params["limit"]), float(params.get("alpha", 1.702))
+        if self.limit <= 0:
+            raise ValueError("limit must be positive")
+        names = {"gate": ".gate", "up": ".up", "down": ".down", **(params.get("names") or {})}
+        self.t_gate, self.t_up, self.t_down = (prefix + names[k] for k in ("gate", "up", "down"))
+
+    def activation_width(self):
+        return 3 * self.intermediate
+
+    def declare(self):
+        return [TensorDecl(self.t_gate, (self.intermediate, self.hidden)), TensorDecl(self.t_up, (self.intermediate, self.hidden)),
+                TensorDecl(self.t_down, (self.hidden, self.intermediate))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.w_gate_up = torch.cat([tensors[self.t_gate], tensors[self.t_up]], 0).contiguous()
+        self.w_down = tensors[self.t_down].contiguous()
+
+    def streamed_weights(self):
+        return [self.w_gate_up, self.w_down]
+
+    def forward(self, x, ctx):
+        ops = self.rt.ops
+        gu = ops.linear(x, self.w_gate_up, meta=ctx.meta)
+        act = torch.empty((gu.shape[0], self.intermediate), dtype=gu.dtype, device=gu.device)
+        ops.clamped_glu(gu, act, self.limit, self.alpha, ctx.meta)
+        return ops.linear(act, self.w_down, meta=ctx.meta)
+
+
+register_part("feed_forward", "clamped_glu", ClampedGLU)

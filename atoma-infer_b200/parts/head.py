@@ -2,7 +2,8 @@
 W is the embedding matrix when the model ties them (:482-486).  No bias.
 
 Parameters: ``vocab``, ``hidden``, ``tensor`` (checkpoint name of the [vocab, hidden] matrix; None: the
-embedding's matrix).
+embedding's matrix), ``scale`` (default 1: the logits are multiplied by it), ``softcap`` (default 0, none: logits <-
+softcap * tanh(logits / softcap), after the scale; float32).
 """
 from __future__ import annotations
 
@@ -20,6 +21,7 @@ class LinearHead(Head):
         super().__init__(params, prefix)
         self.vocab, self.hidden = int(params["vocab"]), int(params["hidden"])
         self.tensor = params.get("tensor")
+        self.scale, self.softcap = float(params.get("scale", 1.0)), float(params.get("softcap") or 0.0)
 
     def declare(self):
         return [TensorDecl(self.tensor, (self.vocab, self.hidden))] if self.tensor else []
@@ -37,7 +39,10 @@ class LinearHead(Head):
         return [self.weight]
 
     def forward(self, h, ctx):
-        return self.rt.ops.linear(h, self.weight, out_dtype=torch.float32, meta=ctx.meta, use_rows=True)
+        logits = self.rt.ops.linear(h, self.weight, out_dtype=torch.float32, meta=ctx.meta, use_rows=True)
+        if self.scale != 1.0 or self.softcap:
+            self.rt.ops.scale_softcap(logits, self.scale, self.softcap, ctx.meta)
+        return logits
 
 
 register_part("head", "linear", LinearHead)

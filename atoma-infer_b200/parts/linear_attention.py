@@ -85,3 +85,77 @@ class GatedLinearAttention(Mixer):
 
 
 register_part("mixer", "gated_linear_attention", GatedLinearAttention)
+
+
+class DecayLinearAttention(Mixer):
+    """Linear attention whose state decays by a constant per head.
+
+    q = act(W_q x), k = act(W_k x) (heads x dim), v = act(W_v x) (heads x vdim), act = SiLU.  Per head
+    S_t = decay_h S_(t-1) + k_t v_t^T and o_t = S_t^T q_t (times ``q_scale``, 1 by default).  The heads side by side are
+    divided by their root mean square over the whole row, multiplied by a weight of the row's size and by sigmoid(W_g x),
+    and projected out.
+
+    State per request (float32, ``cache.state[slot]``): the heads' matrices [heads, dim, vdim], zero at the start; no pages.
+    The recurrence, the norm and the gate are float32 in every mode (the activations are taken in float32 from the
+    projections' outputs); it runs on the kernel of ``GatedLinearAttention`` with the decay as a constant.
+
+    Parameters: ``hidden``, ``heads``, ``dim``, ``vdim``, ``decay`` (one number per head), ``eps``, ``q_scale``, ``names``
+    (suffixes of the tensors: q, k, v, g, o, norm).
+    """
+
+    graph_safe = True  # reads the step's metadata on the device only
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        p = params
+        self.hidden, self.heads, self.dim, self.vdim = int(p["hidden"]), int(p["heads"]), int(p["dim"]), int(p["vdim"])
+        self.eps, self.q_scale = float(p["eps"]), float(p.get("q_scale", 1.0))
+        self.decay = [float(a) for a in p["decay"]]
+        if len(self.decay) != self.heads:
+            raise ValueError(f"{prefix}: {len(self.decay)} decays for {self.heads} heads")
+        self.names = {"q": ".q", "k": ".k", "v": ".v", "g": ".g", "o": ".o", "norm": ".norm", **(p.get("names") or {})}
+        self.qk, self.vg = self.heads * self.dim, self.heads * self.vdim
+
+    def state_bytes(self):
+        return self.heads * self.dim * self.vdim * 4
+
+    def activation_width(self):
+        return 2 * self.qk + 2 * self.vg + 2 * self.vg
+
+    def declare(self):
+        pre, n = self.prefix, self.names
+        return [
+            TensorDecl(pre + n["q"], (self.qk, self.hidden)), TensorDecl(pre + n["k"], (self.qk, self.hidden)),
+            TensorDecl(pre + n["v"], (self.vg, self.hidden)), TensorDecl(pre + n["g"], (self.vg, self.hidden)),
+            TensorDecl(pre + n["o"], (self.hidden, self.vg)), TensorDecl(pre + n["norm"], (self.vg,), init="ones"),
+        ]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        pre, n = self.prefix, self.names
+        t = lambda name: tensors[pre + n[name]]  # noqa: E731
+        self.w_in = torch.cat([t("q"), t("k"), t("v"), t("g")], dim=0).contiguous()  # everything that reads the input
+        self.w_out = t("o").contiguous()
+        self.norm_w = t("norm").to(torch.float32).contiguous()  # widened exactly
+        self.head_decay = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(rt.device).contiguous()
+
+    def streamed_weights(self):
+        return [self.w_in, self.w_out]
+
+    def matrices(self, state):
+        """The per-request state as float32 [slots, heads, dim, vdim]."""
+        return state[:, :self.state_bytes()].view(torch.float32).view(state.shape[0], self.heads, self.dim, self.vdim)
+
+    def forward(self, x, ctx, cache):
+        ops, T, qk, vg = self.rt.ops, ctx.T, self.qk, self.vg
+        proj = ops.linear(x, self.w_in, meta=ctx.meta)
+        o = torch.empty((T, vg), dtype=torch.float32, device=x.device)
+        ops.gla_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vg], None, None, 1.0, self.q_scale,
+                     self.matrices(cache.state), ctx, o, heads=self.heads, dim=self.dim, vdim=self.vdim,
+                     head_decay=self.head_decay, silu=True)
+        y = torch.empty((T, vg), dtype=x.dtype, device=x.device)
+        ops.row_norm_gate(o, proj[:, 2 * qk + vg:], self.norm_w, self.eps, y, ctx.meta, kind="sigmoid")
+        return ops.linear(y, self.w_out, meta=ctx.meta)
+
+
+register_part("mixer", "decay_linear_attention", DecayLinearAttention)

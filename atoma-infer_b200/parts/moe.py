@@ -11,7 +11,9 @@ How it runs: one kernel routes; one sorts the (token, choice) pairs by expert on
 round trip, so a decode step can be captured in a graph); the experts' two linears run as grouped products over
 that order (gate and up stacked, SiLU * up in the epilogue); a last kernel weighs, sums and adds the shared expert.
 
-Parameters: ``hidden``, ``experts``, ``top``, ``intermediate``, ``shared_intermediate`` (0: none), ``names``.
+Parameters: ``hidden``, ``experts``, ``top``, ``intermediate``, ``shared_intermediate`` (0: none), ``names``,
+``router_bias`` (the logits get a learned bias, ``<prefix>.router.b``), ``weights`` (``"all"``, the default: as above;
+``"chosen"``: the softmax over the chosen experts' logits alone).
 Checkpoint tensors: ``<prefix>.router`` [experts, hidden], ``<prefix>.e<j>.{gate,up,down}``,
 ``<prefix>.shared.{gate,up,down}``.
 """
@@ -30,9 +32,12 @@ class RoutedExperts(FeedForward):
         p = params
         self.hidden, self.experts, self.top = int(p["hidden"]), int(p["experts"]), int(p["top"])
         self.intermediate, self.shared = int(p["intermediate"]), int(p.get("shared_intermediate") or 0)
+        self.router_bias, self.over_chosen = bool(p.get("router_bias", False)), p.get("weights", "all") == "chosen"
+        if p.get("weights", "all") not in ("all", "chosen"):
+            raise ValueError(f"weights {p.get('weights')!r} is not known (known: 'all', 'chosen')")
         if not 0 < self.top <= self.experts:
             raise ValueError(f"top ({self.top}) must lie in 1 .. experts ({self.experts})")
-        self.names = {"router": ".router", "expert": ".e{}", "shared": ".shared", "gate": ".gate", "up": ".up", "down": ".down",
+        self.names = {"router": ".router", "router_bias": ".router.b", "expert": ".e{}", "shared": ".shared", "gate": ".gate", "up": ".up", "down": ".down",
                       **(p.get("names") or {})}
 
     def activation_width(self):
@@ -45,6 +50,8 @@ class RoutedExperts(FeedForward):
 
     def declare(self):
         decls = [TensorDecl(self.prefix + self.names["router"], (self.experts, self.hidden))]
+        if self.router_bias:
+            decls.append(TensorDecl(self.prefix + self.names["router_bias"], (self.experts,)))
         for j in list(range(self.experts)) + ([None] if self.shared else []):
             f = self.shared if j is None else self.intermediate
             g, u, d = self._expert(j)
@@ -54,6 +61,8 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.w_router = tensors[self.prefix + self.names["router"]].to(torch.float32).contiguous()  # widened exactly
+        self.b_router = (tensors[self.prefix + self.names["router_bias"]].to(torch.float32).contiguous()
+                         if self.router_bias else None)
         gu, dn = [], []
         for j in range(self.experts):
             g, u, d = self._expert(j)
@@ -73,7 +82,10 @@ class RoutedExperts(FeedForward):
         ops, T = self.rt.ops, ctx.T
         ids = torch.empty((T, self.top), dtype=torch.int32, device=x.device)
         wts = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
-        ops.moe_route(x, self.w_router, ids, wts, ctx.meta)
+        if self.router_bias or self.over_chosen:
+            ops.moe_route(x, self.w_router, ids, wts, ctx.meta, bias=self.b_router, over_chosen=self.over_chosen)
+        else:
+            ops.moe_route(x, self.w_router, ids, wts, ctx.meta)
         shared = None
         if self.shared:
             shared = ops.linear(ops.linear(x, self.ws_gate_up, silu_mul=True, meta=ctx.meta), self.ws_down, meta=ctx.meta)

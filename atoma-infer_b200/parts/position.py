@@ -11,6 +11,7 @@ Parameters: ``head_dim``, ``theta``, ``scaling`` (dict or None; ``rope_type`` ``
 divided by ``factor``), ``rotary_dim``
 (defaults to head_dim), ``exact_frequencies`` (default False: float32 arithmetic as
 above; True: theta^(-2i/rot) taken in float64 and rounded once to float32).
+``interleaved`` (default False): the rotation pairs dimension 2i with 2i + 1.
 ``kind: "none"`` is the same kernel with zero frequencies.
 """
 from __future__ import annotations
@@ -50,6 +51,8 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.theta = float(params.get("theta", 10000.0))
         self.scaling = params.get("scaling")
+        # pairs (x[2i], x[2i + 1]) instead of (x[i], x[i + rot/2]): for mixers that prepare their rows themselves
+        self.interleaved = bool(params.get("interleaved", False))
 
     def _frequencies(self):
         if self.params.get("exact_frequencies"):

@@ -72,15 +72,19 @@ class SideBySide(Mixer):
             view = replace(cache, state=state) if i == self.pager else replace(
                 cache, group=-1, pages=None, num_pages=0, writes=False, state=state, tensors={})
             outs.append(m.forward(x, ctx, view))
-        terms, factors = [], []
+        terms, factors, vector = [], [], None
         for out, scale in zip(outs, self.scales):
             if isinstance(out, PendingSum):
+                if out.rows is not None:
+                    raise ValueError(f"{self.prefix}: a side's result has terms, weights and a vector only")
                 terms += list(out.terms)
                 factors += [scale * out.mult * f for f in out.weights()]
+                if out.vector is not None:  # (a bias of the side's output projection)
+                    vector = scale * out.vector if vector is None else vector + scale * out.vector
             else:
                 terms.append(out)
                 factors.append(scale)
-        return PendingSum(tuple(terms), 1.0, factors=tuple(factors))
+        return PendingSum(tuple(terms), 1.0, vector=vector, factors=tuple(factors))
 
 
 register_part("mixer", "side_by_side", SideBySide)

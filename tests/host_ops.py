@@ -10,6 +10,7 @@ import torch
 
 import plain_bumolix as PB
 import plain_dosovik as PD
+import plain_kulivik as PK
 import plain_tutezen as PT
 import plain_llama as P
 from atoma_infer_b200.csrc.ops import (META_BT_OFFSET, META_BT_STRIDE, META_NUM_ROWS, META_NUM_TOKENS, STATUS_WORDS,
@@ -130,7 +131,7 @@ class HostOps:
 
     def qkv_prepare(self, qkv, ctx, cache, group, q_out, *, nq, nkv, d, dv, dp, page_size, num_pages, store_kv, bias=None,
                     q_norm=None, k_norm=None, eps=0.0, inv_freq=None, rot=0, v_first=None, v_lambda=None, v_out=None,
-                    head_norm=False):
+                    head_norm=False, interleaved=False, q_temp=None):
         self._count()
         meta = ctx.meta
         n = int(meta[META_NUM_TOKENS])
@@ -139,17 +140,30 @@ class HostOps:
         bias, q_norm, k_norm = (t.float() if t is not None else None for t in (bias, q_norm, k_norm))
         rows = qkv[:n].float() + (bias if bias is not None else 0)
         q, k, v = rows[:, :NQ], rows[:, NQ:NQ + NK], rows[:, NQ + NK:]
-        if q_norm is not None:
+        if q_norm is not None and not head_norm:
             q = PD.rms_divide(q, eps) * q_norm
-        if k_norm is not None:
+        if k_norm is not None and not head_norm:
             k = PD.rms_divide(k, eps) * k_norm
         q, k = q.reshape(n, nq, d).clone(), k.reshape(n, nkv, d).clone()
+        weighted = head_norm and q_norm is not None
+        if weighted:  # the norm per head with a shared weight comes before the rotation
+            q, k = PB.rms_divide(q, eps) * q_norm, PB.rms_divide(k, eps) * k_norm
         if inv_freq is not None and rot:
             pos = ctx.positions[:n]
-            q[..., :rot] = P.rope(q[..., :rot], pos, inv_freq)
-            k[..., :rot] = P.rope(k[..., :rot], pos, inv_freq)
-        if head_norm:
+            if interleaved:
+                ang = pos.double()[:, None, None] * inv_freq.double()
+                for x in (q, k):
+                    a, b = x[..., 0:rot:2].double(), x[..., 1:rot:2].double()
+                    x[..., 0:rot:2] = (a * torch.cos(ang) - b * torch.sin(ang)).float()
+                    x[..., 1:rot:2] = (b * torch.cos(ang) + a * torch.sin(ang)).float()
+            else:
+                q[..., :rot] = P.rope(q[..., :rot], pos, inv_freq)
+                k[..., :rot] = P.rope(k[..., :rot], pos, inv_freq)
+        if head_norm and not weighted:
             q, k = PB.rms_divide(q, eps), PB.rms_divide(k, eps)
+        if q_temp:
+            p = ctx.positions[:n].double()
+            q = q * (1.0 + q_temp[0] * torch.log(torch.floor((p + 1) / q_temp[1]) + 1.0)).float()[:, None, None]
         if v_out is not None:
             v_out[:n] = v.to(v_out.dtype)
         if v_first is not None:
@@ -177,7 +191,7 @@ class HostOps:
         out[:n] = PD.poly_norm(z[:n].float(), coef, eps).to(out.dtype)
 
     def attention(self, q, q_stride, cache, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale, rope=None,
-                  chunk=0, sink=False):
+                  chunk=0, sink=False, keep_first=0, softcap=0.0, slopes=None):
         self._count()
         meta = ctx.meta
         n = int(meta[META_NUM_TOKENS])
@@ -187,7 +201,8 @@ class HostOps:
             first = max(0, pos - window + 1) if window else 0
             if chunk:
                 first = max(first, pos - pos % chunk)
-            idx = range(first, pos + 1)
+            idx = list(range(min(keep_first, first) if window else 0)) + list(range(first, pos + 1)) if keep_first else range(first, pos + 1)
+            dist = torch.tensor([float(pos - j) for j in idx])
             pages = [int(meta[off + e * stride + j // page_size]) for j in idx]
             k = torch.stack([cache[p, 0, :, j % page_size] for p, j in zip(pages, idx)]).float()  # [keys, nkv, d]
             v = torch.stack([cache[p, 1, :, j % page_size] for p, j in zip(pages, idx)]).float()
@@ -195,6 +210,10 @@ class HostOps:
             g = nq // nkv
             for h in range(nq):
                 sc = (k[:, h // g] @ qq[h]) * scale
+                if softcap:
+                    sc = softcap * torch.tanh(sc / softcap)
+                if slopes is not None:
+                    sc = sc - slopes[h] * dist
                 if torch.is_tensor(sink):  # a learned sink per head: exp(sink_h) in the denominator
                     w = torch.softmax(torch.cat([sc, sink[h].float().reshape(1)]), 0)[:-1]
                 else:
@@ -232,13 +251,17 @@ class HostOps:
         n = int(meta[META_NUM_TOKENS])
         y[:n] = (y[:n].float() * torch.sigmoid(gate[:n].float())).to(y.dtype)
 
-    def gla_scan(self, q, k, v, z, z_bias, tau, q_scale, state, ctx, o, *, heads, dim, vdim):
+    def gla_scan(self, q, k, v, z, z_bias, tau, q_scale, state, ctx, o, *, heads, dim, vdim, head_decay=None, silu=False):
         self._count()
+        act = PK.silu if silu else (lambda x: x)
         for _, a, b, slot in self._entries(ctx):
             for t in range(a, b):
-                qt, kt = q[t].float().view(heads, dim) * q_scale, k[t].float().view(heads, dim)
-                vt = v[t].float().view(heads, vdim)
-                decay = torch.exp(torch.nn.functional.logsigmoid(z[t] + z_bias) / tau).view(heads, dim)  # no underflow below the power
+                qt, kt = act(q[t].float()).view(heads, dim) * q_scale, act(k[t].float()).view(heads, dim)
+                vt = act(v[t].float()).view(heads, vdim)
+                if head_decay is not None:
+                    decay = head_decay[:, None].expand(heads, dim)
+                else:
+                    decay = torch.exp(torch.nn.functional.logsigmoid(z[t] + z_bias) / tau).view(heads, dim)  # no underflow below the power
                 for h in range(heads):
                     S = decay[h][:, None] * state[slot, h] + torch.outer(kt[h], vt[h])
                     state[slot, h] = S
@@ -353,9 +376,19 @@ class HostOps:
         n = int(meta[META_NUM_TOKENS])
         out[:n] = {"gelu_tanh": PT.gelu_tanh, "relu2": PB.relu_squared}[kind](z[:n].float()).to(out.dtype)
 
-    def moe_route(self, h, w_router, ids, wts, meta):
+    def moe_route(self, h, w_router, ids, wts, meta, bias=None, over_chosen=False):
         self._count()
         n = int(meta[META_NUM_TOKENS])
+        if bias is not None or over_chosen:
+            z = h[:n].float() @ w_router.T + (bias if bias is not None else 0)
+            if over_chosen:
+                idx, wt = PK.route(z, ids.shape[1])
+            else:
+                sc = torch.softmax(z, -1)
+                wt, idx = torch.topk(sc, ids.shape[1], dim=-1)
+                wt = wt / wt.sum(-1, keepdim=True)
+            ids[:n], wts[:n] = idx.to(torch.int32), wt.float()
+            return
         idx, wt = PT.route(h[:n].float(), w_router, ids.shape[1])
         ids[:n], wts[:n] = idx.to(torch.int32), wt
 
@@ -373,6 +406,67 @@ class HostOps:
             if shared is not None:
                 acc = acc + shared[t].float()
             out[t] = acc.to(out.dtype)
+
+    # -- blocks that norm and gate a sublayer's result, with the mixer's input shifted toward the token before
+    def norm_shift(self, resid, w, eps, ctx, *, shift=None, state=None, h=None, hs=None, last=None):
+        self._count()
+        for k, a, b, slot in self._entries(ctx):
+            if a == b:
+                continue
+            hv = P.rms_norm(resid[a:b], w, eps).float()
+            if h is not None:
+                h[a:b] = hv.to(h.dtype)
+            if last is not None:
+                last[k] = hv[-1]
+            if hs is not None:
+                if shift is None:
+                    hs[a:b] = hv.to(hs.dtype)
+                    continue
+                first = state[slot].clone() if (state is not None and int(ctx.positions[a]) > 0) else torch.zeros_like(hv[0])
+                before = torch.cat([first[None], hv[:-1]], 0)
+                hs[a:b] = (hv + (before - hv) * shift).to(hs.dtype)
+
+    def gated_norm_add(self, resid, pending, gate, gate_bias, w, eps, ctx, *, next_norm=None, keep=None):
+        self._count()
+        n = int(ctx.meta[META_NUM_TOKENS])
+        y = torch.zeros_like(resid[:n])
+        for t, f in zip(pending.terms, pending.weights()):
+            y = y + f * t[:n].float()
+        y = y * pending.mult
+        if pending.vector is not None:
+            y = y + pending.vector
+        y = y * torch.sigmoid(gate[:n].float() + (gate_bias if gate_bias is not None else 0))
+        resid[:n] += P.rms_norm(y, w, eps).float()
+        if next_norm is not None:
+            next_norm[2][:n] = P.rms_norm(resid[:n], next_norm[0], next_norm[1]).to(next_norm[2].dtype)
+        if keep is not None:
+            for k, a, b, slot in self._entries(ctx):
+                if b > a:
+                    keep[1][slot] = keep[0][k]
+
+    def clamped_glu(self, gu, out, limit, alpha, meta):
+        self._count()
+        n, f = int(meta[META_NUM_TOKENS]), out.shape[1]
+        g = gu[:n, :f].float().clamp(max=limit)
+        u = gu[:n, f:].float().clamp(-limit, limit)
+        out[:n] = (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out.dtype)
+
+    def head_gate(self, y, gate, meta):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        y[:n] = (y[:n].float() * torch.sigmoid(gate[:n].float())[:, :, None]).to(y.dtype)
+
+    def row_norm_gate(self, o, gate, w, eps, out, meta, kind="sigmoid"):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        g = gate[:n].float()
+        out[:n] = (PB.rms_divide(o[:n], eps) * w * (torch.sigmoid(g) if kind == "sigmoid" else PB.silu(g))).to(out.dtype)
+
+    def scale_softcap(self, logits, scale, cap, meta):
+        self._count()
+        n = int(meta[META_NUM_ROWS])
+        z = logits[:n] * scale
+        logits[:n] = cap * torch.tanh(z / cap) if cap else z
 
     def sample(self, logits, temperature, top_k, top_p, seed, step, out, num_rows=None, slots=None):
         self._count()
