@@ -48,6 +48,10 @@ extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 //    the launch and is zero again after it.
 // Before the dependency wait the kernel only touches what no kernel of the step writes: the
 // step's metadata (block table, positions) and keys and values of earlier steps.
+// SCORES: the instantiation for capped scores, a bias by distance and a window that keeps the first keep_first keys (see
+// attn_prefill_kernel); the kept keys are tiles of the first split, ahead of its share of the window; `scale_log2` is
+// then the plain scale.
+template <bool SCORES>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16* __restrict__ q, int q_stride,
                    bf16* __restrict__ cache, CacheLayout L,
@@ -55,7 +59,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
                    const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
                    int store_kv, int nq, int window, int chunk, int sink, const float* __restrict__ sink_values, float scale_log2,
-                   int num_pages, int splits, int cluster_merge, int* __restrict__ status) {
+                   int num_pages, int splits, int cluster_merge, int keep_first, float softcap,
+                   const float* __restrict__ slopes, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // tiles start on 1024-byte boundaries: TMA writes them with the 128-byte swizzle, whose pattern follows the address
     unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -92,13 +97,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
     const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
     const size_t v_off = (size_t)L.num_kv_heads * ps * D, page_stride = 2 * v_off, head_off = (size_t)kvh * ps * D;
     bf16* mine = tiles + warp * DEC_WARP_ELEMS;
-    const int ntiles = lo < hi ? (hi - lo + DEC_KT - 1) / DEC_KT : 0;
+    // kept first keys (0 .. kept - 1, all before the window): tiles of the first split, ahead of its own
+    const int kept = SCORES && window > 0 && chunk <= 0 && split == 0 ? min(keep_first, kstart) : 0;
+    const int ktiles = SCORES ? (kept + DEC_KT - 1) / DEC_KT : 0;
+    const int ntiles = ktiles + (lo < hi ? (hi - lo + DEC_KT - 1) / DEC_KT : 0);
+    auto tile_k0 = [&](int t) { return SCORES && t < ktiles ? t * DEC_KT : lo + (t - ktiles) * DEC_KT; };
+    auto tile_hi = [&](int t) { return SCORES && t < ktiles ? kept : hi; };
     auto fetch_pages = [&](int t, int (&pg)[RPL]) {
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
-            int pos = lo + t * DEC_KT + (lane + 32 * i) / PAIRS;
+            int pos = tile_k0(t) + (lane + 32 * i) / PAIRS;
             pg[i] = -1;
-            if (pos < hi) pg[i] = __ldg(bt + (ps_shift >= 0 ? pos >> ps_shift : pos / ps));
+            if (pos < tile_hi(t)) pg[i] = __ldg(bt + (ps_shift >= 0 ? pos >> ps_shift : pos / ps));
         }
     };
     auto load_tile = [&](int t, int stage, const int (&pg)[RPL]) {
@@ -145,10 +155,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
             int idx = lane + 32 * i, r = idx / PAIRS, c = (idx % PAIRS) * 16;
-            int pos = lo + t * DEC_KT + r;
+            int pos = tile_k0(t) + r;
             int o0 = toff(r, c), o1 = toff(r, c + 8);
             int page = pg[i];
-            if (pos < hi && (page <= 0 || page >= num_pages)) {
+            if (pos < tile_hi(t) && (page <= 0 || page >= num_pages)) {
                 atomicExch(&status[STATUS_BAD_PAGE], 1 + pos);
                 page = -1;
             }
@@ -173,7 +183,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
     if (live && warp + DEC_WARPS < ntiles) fetch_pages(warp + DEC_WARPS, pg_nxt);
     // The newest position (kv_len - 1) is written during this step, by the kernel before this one
     // or by this block; every other key is older than the step and may be fetched at once.
-    const bool first_is_old = live && warp < ntiles && lo + (warp + 1) * DEC_KT <= kv_len - 1;
+    const bool first_is_old = live && warp < ntiles && tile_k0(warp) + DEC_KT <= kv_len - 1;
     if (first_is_old) load_tile(warp, 0, pg_cur);
     cp_async_commit();
 
@@ -283,13 +293,22 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
         __syncwarp();
         float s[DEC_NK][4];
         qk_tile<DEC_NK>(s, qf, qtile, ktile, lane);
-        const int k0 = lo + t * DEC_KT;
+        const int k0 = tile_k0(t), k1 = tile_hi(t);
 #pragma unroll
         for (int n = 0; n < DEC_NK; ++n)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 int key = k0 + n * 8 + (lane & 3) * 2 + (c & 1);
-                s[n][c] = key < hi ? s[n][c] * scale_log2 : -INFINITY;
+                if constexpr (SCORES) {
+                    float v = s[n][c] * scale_log2;
+                    if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+                    // row (lane >> 2) + 8 (c >> 1) of the tile is that head of the group
+                    const int r = (lane >> 2) + 8 * (c >> 1);
+                    const float sl = slopes && r < G ? slopes[kvh * G + r] * LOG2E : 0.f;
+                    s[n][c] = key < k1 ? v * LOG2E - sl * (float)(newest - key) : -INFINITY;
+                } else {
+                    s[n][c] = key < k1 ? s[n][c] * scale_log2 : -INFINITY;
+                }
             }
         softmax_tile<DEC_NK>(s, m, l, o);
         pv_tile<DEC_NK>(o, s, vtile, lane);
@@ -472,11 +491,17 @@ constexpr int PF_STAGES = 2;
 constexpr size_t PF_SMEM = (size_t)(PF_ROWS * LDS + PF_STAGES * 2 * PF_KT * LDS) * sizeof(bf16);
 }  // namespace
 
+// SCORES: the instantiation for scores that are capped (softcap > 0: s <- softcap * tanh(s / softcap)), biased by distance
+// (slopes[h] * (query position - key position) taken off) or masked by a window that keeps the first keep_first keys of a
+// request visible; the kept keys come as tiles of their own ahead of the window's, through a second slice of the block
+// table.  `scale_log2` is then the plain scale (the conversion to base 2 follows the cap).
+template <bool SCORES>
 __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache, CacheLayout L,
                     const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                     const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, int chunk, int sink,
-                    const float* __restrict__ sink_values, float scale_log2, int num_pages, int bt_cap, int* __restrict__ status) {
+                    const float* __restrict__ sink_values, float scale_log2, int num_pages, int bt_cap, int keep_first,
+                    float softcap, const float* __restrict__ slopes, int kept_cap, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
     bf16* kv = qtile + PF_ROWS * LDS;
@@ -508,7 +533,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     if (chunk > 0) kbeg = max(kbeg, p_first - p_first % chunk);  // the first row's chunk starts earliest
     const int kend = p_last + 1;
     const int k_first = (kbeg / PF_KT) * PF_KT;
-    const int ntiles = (kend - k_first + PF_KT - 1) / PF_KT;
+    const int ntiles_window = (kend - k_first + PF_KT - 1) / PF_KT;
     const int page_lo = kbeg / L.page_size;
     int page_cnt = (kend - 1) / L.page_size - page_lo + 1;
     if (page_cnt > bt_cap) {
@@ -517,10 +542,21 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     }
     stage_block_table(bt_s, bt, page_lo, page_cnt, num_pages, tid, 128, status);
     const int kend_s = min(kend, (page_lo + page_cnt) * L.page_size);
+    // kept first keys: 0 .. kept - 1, all of them before the first row's window; their pages behind the window's in bt_s
+    int kept = 0, tiles_kept = 0;
+    if constexpr (SCORES) {
+        kept = window > 0 && chunk <= 0 ? min(min(keep_first, kbeg), kept_cap * L.page_size) : 0;
+        tiles_kept = (kept + PF_KT - 1) / PF_KT;
+        if (kept > 0) stage_block_table(bt_s + bt_cap, bt, 0, (kept + L.page_size - 1) / L.page_size, num_pages, tid, 128, status);
+    }
+    const int ntiles = tiles_kept + ntiles_window;
     __syncthreads();  // the Q tile and the table slice are written
     auto load_tile = [&](int t, int stage) {
         bf16* k = kv + stage * 2 * PF_KT * LDS;
-        load_kv_tile(k, k + PF_KT * LDS, cache, L, bt_s, page_lo, kvh, k_first + t * PF_KT, PF_KT, kbeg, kend_s, tid, 128);
+        if (SCORES && t < tiles_kept)
+            load_kv_tile(k, k + PF_KT * LDS, cache, L, bt_s + bt_cap, 0, kvh, t * PF_KT, PF_KT, 0, kept, tid, 128);
+        else
+            load_kv_tile(k, k + PF_KT * LDS, cache, L, bt_s, page_lo, kvh, k_first + (t - tiles_kept) * PF_KT, PF_KT, kbeg, kend_s, tid, 128);
     };
     load_tile(0, 0);
     cp_async_commit();
@@ -551,6 +587,14 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     // with chunks: below this key some row of the warp sees nothing although the key is not after it
     const int warp_cmax = chunk > 0 && warp_pmax >= 0 ? warp_pmax - warp_pmax % chunk : 0;
     const bool has_padding = warp_last_tok_all >= nt;
+    float slope2[PF_MT][2];  // the rows' slopes, in base 2
+    if constexpr (SCORES) {
+#pragma unroll
+        for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                slope2[mt][h] = slopes ? slopes[kvh * G + (wrow + mt * 16 + (lane >> 2) + 8 * h) % G] * LOG2E : 0.f;
+    }
 
     float m[PF_MT][2], l[PF_MT][2];
     float o[PF_MT][DTILES][4];
@@ -578,8 +622,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
             cp_async_wait<0>();
         }
         __syncthreads();
-        const int k0 = k_first + t * PF_KT;
-        if (k0 <= warp_pmax && k0 + PF_KT > warp_kmin) {  // the tile holds keys some row of this warp sees
+        const bool kept_tile = SCORES && t < tiles_kept;
+        const int k0 = kept_tile ? t * PF_KT : k_first + (t - tiles_kept) * PF_KT;
+        if ((k0 <= warp_pmax && k0 + PF_KT > warp_kmin) || (kept_tile && warp_pmax >= 0)) {  // the tile holds keys some row of this warp sees
             const bf16* ktile = kv + stage * 2 * PF_KT * LDS;
             const bf16* vtile = ktile + PF_KT * LDS;
             float s[PF_MT][PF_NK][4];
@@ -617,12 +662,19 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         bool vis = true;
-                        if (need_mask) {
-                            int key = k0 + n * 8 + (lane & 3) * 2 + (c & 1);
-                            int p = prow[mt][c >> 1];
-                            vis = key <= p && (window <= 0 || p - key < window) && (chunk <= 0 || key >= p - p % chunk);
+                        const int key = k0 + n * 8 + (lane & 3) * 2 + (c & 1);
+                        const int p = prow[mt][c >> 1];
+                        if constexpr (SCORES) {
+                            // a tile of kept keys holds nothing else; a tile of the window nothing before the window's start
+                            vis = key <= p && (window <= 0 || p - key < window || key < keep_first) &&
+                                  (chunk <= 0 || key >= p - p % chunk) && (kept_tile ? key < kept : (kept <= 0 || key >= kbeg));
+                            float v = s[mt][n][c] * scale_log2;
+                            if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+                            s[mt][n][c] = vis ? v * LOG2E - slope2[mt][c >> 1] * (float)(p - key) : -INFINITY;
+                        } else {
+                            if (need_mask) vis = key <= p && (window <= 0 || p - key < window) && (chunk <= 0 || key >= p - p % chunk);
+                            s[mt][n][c] = vis ? s[mt][n][c] * scale_log2 : -INFINITY;
                         }
-                        s[mt][n][c] = vis ? s[mt][n][c] * scale_log2 : -INFINITY;
                     }
                 softmax_tile<PF_NK>(s[mt], m[mt], l[mt], o[mt]);
             }
@@ -690,8 +742,8 @@ extern "C" int attn_decode_blocks_per_sm() {
     if (!cached[dev]) {
         int n = 0;
         const size_t smem = DEC_SMEM + 1024;
-        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_kernel, DEC_WARPS * 32, smem) != cudaSuccess || n < 1)
+        if (cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_kernel<false>, DEC_WARPS * 32, smem) != cudaSuccess || n < 1)
             n = DEC_BLOCKS_PER_SM;
         cached[dev] = n;
     }
@@ -712,6 +764,12 @@ extern "C" int attn_decode_max_splits(int nq, int nkv) {
     return (int)(DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) / ((size_t)G * 2 * sizeof(float)));
 }
 
+extern "C" int attn_prefill_scores(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                   const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
+                                   int page_size, int num_pages, int window, int chunk, int sink, const float* sink_values,
+                                   float scale, int max_context, int keep_first, float softcap, const float* slopes, int* status,
+                                   cudaStream_t stream);
+
 // chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0);
 // sink: one more term in the softmax's denominator, a key of score 0 without a value.
 // sink_values (one float per query head, or null): the sink's score per head instead of 0.
@@ -719,7 +777,21 @@ extern "C" int attn_prefill_sinks(const void* q, int q_stride, const void* cache
                                   const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
                                   int page_size, int num_pages, int window, int chunk, int sink, const float* sink_values,
                                   float scale, int max_context, int* status, cudaStream_t stream) {
+    return attn_prefill_scores(q, q_stride, cache, meta, group, cu_tokens, ctx_lens, out, S, max_q_len, nq, nkv, page_size, num_pages,
+                               window, chunk, sink, sink_values, scale, max_context, 0, 0.f, nullptr, status, stream);
+}
+
+// keep_first (with a window): the first keep_first keys of a request stay visible behind the window.  softcap > 0: a score
+// s becomes softcap * tanh(s / softcap).  slopes (one float per query head, or null): slopes[h] * (query position - key
+// position) is taken off the score.  Without any of them the plain instantiation runs.
+extern "C" int attn_prefill_scores(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                   const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
+                                   int page_size, int num_pages, int window, int chunk, int sink, const float* sink_values,
+                                   float scale, int max_context, int keep_first, float softcap, const float* slopes, int* status,
+                                   cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0) return 0;
+    if (window <= 0 || chunk > 0) keep_first = 0;
+    const bool scores = keep_first > 0 || softcap > 0.f || slopes != nullptr;
     if (nq % nkv || nq / nkv > 16) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
     int tpt = PF_ROWS / (nq / nkv);
@@ -728,17 +800,25 @@ extern "C" int attn_prefill_sinks(const void* q, int q_stride, const void* cache
     int span = window > 0 ? min(max_context, window + tpt + PF_KT) : max_context;
     if (chunk > 0) span = min(span, chunk + tpt + PF_KT);
     int bt_cap = span / page_size + 2;
-    size_t smem = PF_SMEM + (size_t)bt_cap * sizeof(int);
+    // (the kept keys' pages: a second slice behind the first; what does not fit in shared memory is not kept and raises
+    // the status word in the kernel's place)
+    int kept_cap = keep_first > 0 ? (min(keep_first, max_context) + page_size - 1) / page_size : 0;
+    size_t smem = PF_SMEM + (size_t)(bt_cap + kept_cap) * sizeof(int);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
-    static size_t configured = 0;  // grows only, and is not set again inside a stream capture once large enough
-    if (smem > configured) {
-        cudaError_t err = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t configured[2] = {0, 0};  // grows only, and is not set again inside a stream capture once large enough
+    if (smem > configured[scores]) {
+        cudaError_t err = scores ? cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                 : cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
-        configured = smem;
+        configured[scores] = smem;
     }
-    return (int)launch_kernel(attn_prefill_kernel, grid, 128, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, L, meta,
+    if (scores)
+        return (int)launch_kernel(attn_prefill_kernel<true>, grid, 128, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, L,
+                                  meta, group, cu_tokens, ctx_lens, (bf16*)out, nq, window, chunk, sink, sink_values, scale, num_pages,
+                                  bt_cap, keep_first, softcap, slopes, kept_cap, status);
+    return (int)launch_kernel(attn_prefill_kernel<false>, grid, 128, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, L, meta,
                               group, cu_tokens, ctx_lens, (bf16*)out, nq, window, chunk, sink, sink_values, scale * LOG2E, num_pages,
-                              bt_cap, status);
+                              bt_cap, 0, 0.f, nullptr, 0, status);
 }
 
 extern "C" int attn_prefill_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
@@ -812,11 +892,30 @@ extern "C" int attn_decode_flat(const void* q, int q_stride, const void* cache, 
 // splits > 1, and `counters`: S * nkv ints, zero before the first launch (the kernel leaves them zero).  `inv_freq` (rot/2 floats) switches the fused rotation on: q is
 // then the unrotated projection row and, with store_kv, the new key and value are written here too.
 // sink_values (one float per query head, or null): the sink's score per head instead of 0.
+extern "C" int attn_decode_scores(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                  const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
+                                  const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
+                                  int num_pages, int window, int chunk, int sink, const float* sink_values, float scale, int splits,
+                                  int cluster_merge, int max_context, int keep_first, float softcap, const float* slopes,
+                                  int* status, cudaStream_t stream);
+
 extern "C" int attn_decode_sinks(const void* q, int q_stride, const void* cache, const int* meta, int group,
                                  const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
                                  const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
                                  int num_pages, int window, int chunk, int sink, const float* sink_values, float scale, int splits,
                                  int cluster_merge, int max_context, int* status, cudaStream_t stream) {
+    return attn_decode_scores(q, q_stride, cache, meta, group, cu_tokens, positions, out, scratch, counters, inv_freq, rot, store_kv,
+                              S, nq, nkv, page_size, num_pages, window, chunk, sink, sink_values, scale, splits, cluster_merge,
+                              max_context, 0, 0.f, nullptr, status, stream);
+}
+
+// keep_first, softcap, slopes: as for attn_prefill_scores (not together with the fused rotation).
+extern "C" int attn_decode_scores(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                  const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
+                                  const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
+                                  int num_pages, int window, int chunk, int sink, const float* sink_values, float scale, int splits,
+                                  int cluster_merge, int max_context, int keep_first, float softcap, const float* slopes,
+                                  int* status, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (nq % nkv || nq / nkv > 16 || splits < 1) return (int)cudaErrorInvalidValue;
     if (splits == 1) cluster_merge = 0;
@@ -835,10 +934,14 @@ extern "C" int attn_decode_sinks(const void* q, int q_stride, const void* cache,
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return (int)cudaErrorInvalidDevice;
     if (dev >= 64 || !configured[dev]) {
-        cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
         if (dev < 64) configured[dev] = true;
     }
+    if (window <= 0 || chunk > 0) keep_first = 0;
+    const bool scores = keep_first > 0 || softcap > 0.f || slopes != nullptr;
+    if (scores && inv_freq) return (int)cudaErrorInvalidValue;  // (the fused rotation is the plain instantiation's)
     // Page loads by TMA when a page's rows tile a warp's 32-key tile and start on its boundaries.
     CUtensorMap map;
     memset(&map, 0, sizeof map);
@@ -884,9 +987,15 @@ extern "C" int attn_decode_sinks(const void* q, int q_stride, const void* cache,
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel, map, use_tma, (bf16*)q, q_stride, (bf16*)cache, L, meta, group,
+    if (scores)
+        return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel<true>, map, 0, (bf16*)q, q_stride, (bf16*)cache, L, meta, group,
+                                       cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
+                                       window, chunk, sink, sink_values, scale, num_pages, splits, cluster_merge, keep_first,
+                                       softcap, slopes, status);
+    return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel<false>, map, use_tma, (bf16*)q, q_stride, (bf16*)cache, L, meta, group,
                                    cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
-                                   window, chunk, sink, sink_values, scale * LOG2E, num_pages, splits, cluster_merge, status);
+                                   window, chunk, sink, sink_values, scale * LOG2E, num_pages, splits, cluster_merge, 0, 0.f,
+                                   nullptr, status);
 }
 
 extern "C" int attn_decode_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,

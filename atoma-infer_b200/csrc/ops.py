@@ -91,6 +91,7 @@ class CudaOps:
         self.pdl = {"0": 0, "1": 1, "linear": 2, "linear+norm": 6}.get(mode, 6)
         self.fused_rope = True  # the decode attention rotates q and k and writes the new key and value itself
         self.masked_fast_attention = True  # chunk masks and sinks on the tensor-core attention kernels (False: on the plain one; a test lever)
+        self.scored_fast_attention = True  # likewise score caps, distance slopes and windows that keep the first tokens
         # Few-row linears go to the persistent, TMA-fed kernel (kernels/linear_stream.cu) where it is the faster one
         # (see _stream_linear); ATOMA_INFER_STREAM_LINEAR=0 keeps them all on the kernel that loads weights into
         # fragments directly (kernels/linear_bf16.cu).  The kernel tests set the attribute.
@@ -459,23 +460,25 @@ class CudaOps:
         T, S = ctx.T, ctx.S
         if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != nq or not slopes.is_contiguous()):
             raise KernelError("distance slopes are one contiguous float32 number per query head")
-        if (keep_first and window) or softcap or slopes is not None:
-            if rope is not None:
-                raise KernelError("the fused rotation does not go with kept first tokens, a score cap or distance slopes")
-            if self._attention_scores(q, q_stride, cache_layer, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale,
-                                      chunk, sink, int(keep_first) if window else 0, float(softcap), slopes):
-                return
         # a learned sink: one float32 score per query head (a tensor) instead of the score 0 (True)
         sinks = sink if torch.is_tensor(sink) else None
         sink = sinks is not None or bool(sink)
         if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nq or not sinks.is_contiguous()):
             raise KernelError("learned sinks are one contiguous float32 score per query head")
-        if (chunk or sink) and self.fast_attention(q.dtype, d, nq, nkv, q_stride) and not self.masked_fast_attention:
-            self._check(self.lib.attn_generic_sinks(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
-                                                    _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
-                                                    num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
-                                                    ctypes.c_float(scale), _p(self.status), self._stream()), "attn_generic")
+        keep_first = int(keep_first) if window and not chunk else 0
+        scored = bool(keep_first or softcap or slopes is not None)
+        if scored and rope is not None:
+            raise KernelError("the fused rotation does not go with kept first tokens, a score cap or distance slopes")
+        extra = (keep_first, ctypes.c_float(float(softcap)), _p(slopes))
+        if scored and not self.scored_fast_attention:  # (a test lever: the plain kernel in both number formats)
+            self._attention_scores(q, q_stride, cache_layer, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale,
+                                   chunk, sinks if sinks is not None else sink, keep_first, float(softcap), slopes)
             return
+        if (chunk or sink) and self.fast_attention(q.dtype, d, nq, nkv, q_stride) and not self.masked_fast_attention:
+            self._attention_scores(q, q_stride, cache_layer, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale,
+                                   chunk, sinks if sinks is not None else sink, keep_first, float(softcap), slopes)
+            return
+
         if rope is not None and not (ctx.decode_only and self.fast_attention(q.dtype, d, nq, nkv, q_stride)):
             raise KernelError("fused rotation exists for decode steps on the bfloat16 fast path only")
         if self.fast_attention(q.dtype, d, nq, nkv, q_stride):
@@ -483,7 +486,7 @@ class CudaOps:
             if ctx.decode_only:
                 inv_freq, rot, store = rope if rope is not None else (None, 0, False)
                 # a chunk bounds the keys of a request and a sink is one more partial result: both go with fixed splits
-                flat_blocks = 0 if (chunk or sink) else self._decode_flat_blocks(lib, d, S, nkv)
+                flat_blocks = 0 if (chunk or sink or scored) else self._decode_flat_blocks(lib, d, S, nkv)
                 if flat_blocks:
                     # large batch: as many blocks as the GPU holds share all key tiles evenly
                     n = lib.attn_decode_flat_scratch_floats(S, nq, nkv, flat_blocks)
@@ -498,7 +501,7 @@ class CudaOps:
                     return
                 seen = min(ctx.max_context, chunk) if chunk else ctx.max_context  # most keys a request reads
                 if window:
-                    seen = min(seen, window)
+                    seen = min(seen, window + keep_first)
                 splits = self.decode_splits(S, nkv, seen, lib.attn_decode_blocks_per_sm())
                 # the splits merge inside a thread-block cluster when they fit one, else through scratch
                 if S <= SKINNY_MAX_ROWS:
@@ -508,13 +511,13 @@ class CudaOps:
                 scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
                 if not cluster and S * nkv > self._counters.numel():
                     raise KernelError(f"decode attention: {S} requests x {nkv} heads exceed the split counters")
-                self._check(lib.attn_decode_sinks(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                                  _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
-                                                  rot, int(store), S, nq, nkv, page_size, num_pages,
-                                                  window, int(chunk), int(bool(sink)), _p(sinks), ctypes.c_float(scale), splits,
-                                                  int(cluster), ctx.max_context, _p(self.status), self._stream()),
+                self._check(lib.attn_decode_scores(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                                   _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
+                                                   rot, int(store), S, nq, nkv, page_size, num_pages,
+                                                   window, int(chunk), int(bool(sink)), _p(sinks), ctypes.c_float(scale), splits,
+                                                   int(cluster), ctx.max_context, *extra, _p(self.status), self._stream()),
                             "attn_decode")
-            elif self._prefill_tc(d, page_size, nq, nkv) is not None:
+            elif not scored and self._prefill_tc(d, page_size, nq, nkv) is not None:
                 tc = self._prefill_tc(d, page_size, nq, nkv)
                 self._check(tc.attn_prefill_tc_sinks(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                                      _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
@@ -522,23 +525,18 @@ class CudaOps:
                                                      ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
                             "attn_prefill_tc")
             else:
-                self._check(lib.attn_prefill_sinks(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                                   _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
-                                                   page_size, num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
-                                                   ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
+                self._check(lib.attn_prefill_scores(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                                    _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
+                                                    page_size, num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
+                                                    ctypes.c_float(scale), ctx.max_context, *extra, _p(self.status), self._stream()),
                             "attn_prefill")
             return
-        if d > 512:
-            raise KernelError(f"head size {d} is not supported (at most 512)")
-        self._check(self.lib.attn_generic_sinks(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
-                                                _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
-                                                num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
-                                                ctypes.c_float(scale), _p(self.status), self._stream()), "attn_generic")
+        self._attention_scores(q, q_stride, cache_layer, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale, chunk,
+                               sinks if sinks is not None else sink, keep_first, float(softcap), slopes)
 
     def _attention_scores(self, q, q_stride, cache_layer, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale,
                           chunk, sink, keep_first, softcap, slopes) -> bool:
-        """Attention whose scores are capped, biased by distance, or masked by a window that keeps the first tokens: on the
-        plain kernel (both number formats)."""
+        """The plain attention kernel (both number formats, any head size up to 512), with every option."""
         sinks = sink if torch.is_tensor(sink) else None
         if d > 512:
             raise KernelError(f"head size {d} is not supported (at most 512)")

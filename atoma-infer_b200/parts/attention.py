@@ -179,9 +179,14 @@ class Attention(Mixer):
                                + ([tensors[pre + n["gate"]]] if self.gate or self.head_gate else []), dim=0).contiguous()
         self.w_o = tensors[pre + n["o"]].contiguous()
         self.position.bind(tensors, rt)
+        f32 = lambda name: tensors[pre + n[name]].to(torch.float32).contiguous()  # noqa: E731  (exact widening)
+        self.b_o = f32("o_bias") if self.out_bias else None
+        self.sinks = f32("sink") if self.learned_sink else None
+        # slope_h = 2^(-8 (h + 1) / heads), taken in float64 and rounded once
+        self.slopes = (torch.tensor([2.0 ** (-8.0 * (h + 1) / self.num_heads) for h in range(self.num_heads)], dtype=torch.float64)
+                       .to(torch.float32).to(rt.device).contiguous() if self.distance_bias else None)
         if not self.prepared:
             return
-        f32 = lambda name: tensors[pre + n[name]].to(torch.float32).contiguous()  # noqa: E731  (exact widening)
         # Biases and norm weights stay as the loader left them when that is one type for all (bfloat16 from a bfloat16
         # checkpoint: the kernel widens them, exactly, as it reads them); else all are widened here.
         normed = self.qk_norm is not None or self.head_norm_weight
@@ -191,11 +196,6 @@ class Attention(Mixer):
         self.b_qkv = torch.cat([get("q_bias"), get("k_bias"), get("v_bias")]).contiguous() if self.bias else None
         self.w_q_norm, self.w_k_norm = (get("q_norm"), get("k_norm")) if normed else (None, None)
         self.v_lambda = f32("v_mix").reshape(1) if self.v_mix is not None else None
-        self.b_o = f32("o_bias") if self.out_bias else None
-        self.sinks = f32("sink") if self.learned_sink else None
-        # slope_h = 2^(-8 (h + 1) / heads), taken in float64 and rounded once
-        self.slopes = (torch.tensor([2.0 ** (-8.0 * (h + 1) / self.num_heads) for h in range(self.num_heads)], dtype=torch.float64)
-                       .to(torch.float32).to(rt.device).contiguous() if self.distance_bias else None)
         # [taps, channels] over the fused [q | k | v] rows: neighbouring threads read neighbouring weights
         self.conv_w = (torch.cat([tensors[pre + n[x] + n["conv"]] for x in ("q", "k", "v")], 0).to(torch.float32).t().contiguous()
                        if self.taps else None)
@@ -211,6 +211,11 @@ class Attention(Mixer):
         return {"kind": "attention", "w_qkv": self.w_qkv, "w_o": self.w_o, "hidden": self.hidden,
                 "num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim,
                 "scale": self.scale, "window": int(self.window or 0), "inv_freq": rotary[0], "rotary_dim": rotary[1]}
+
+    def _score_options(self):
+        """What changes a score or the mask beyond window, chunk and sink, as keyword arguments of ``ops.attention``."""
+        return {k: v for k, v in (("keep_first", self.keep_first), ("softcap", self.softcap), ("slopes", self.slopes))
+                if v is not None and (torch.is_tensor(v) or v)}
 
     def _forward_prepared(self, x, ctx, cache):
         ops = self.rt.ops
@@ -247,8 +252,7 @@ class Attention(Mixer):
                         **({"interleaved": True} if getattr(self.position, "interleaved", False) else {}),
                         **({"q_temp": (float(self.q_temp["coef"]), int(self.q_temp["every"]))} if self.q_temp else {}))
         out = torch.empty((ctx.T, H * dp), dtype=x.dtype, device=x.device)
-        scores = {k: v for k, v in (("keep_first", self.keep_first), ("softcap", self.softcap), ("slopes", self.slopes))
-                  if v is not None and (torch.is_tensor(v) or v)}
+        scores = self._score_options()
         ops.attention(q, H * dp, cache.pages, ctx, cache.group, out, H, G, dp, cache.page_size, cache.num_pages,
                       int(self.window or 0), self.scale, chunk=self.chunk, sink=self.sinks if self.learned_sink else self.sink,
                       **scores)
@@ -267,7 +271,8 @@ class Attention(Mixer):
         # In a decode step the attention kernel can rotate q and write the new key and value itself.
         rope = None
         fast = getattr(ops, "fast_attention", None)
-        if self.chunk or self.sink:
+        scores = self._score_options()
+        if self.chunk or self.sink or scores:
             fast = None  # the fused rotation is the plain decode kernel's
         if ctx.decode_only and getattr(ops, "fused_rope", True) and fast and fast(qkv.dtype, self.head_dim, self.num_heads, self.num_kv_heads, qkv.shape[1]):
             rotary = self.position.rotary()
@@ -279,8 +284,10 @@ class Attention(Mixer):
         out = torch.empty((ctx.T, self.q_size), dtype=x.dtype, device=x.device)
         ops.attention(qkv, qkv.shape[1], cache.pages, ctx, cache.group, out, self.num_heads, self.num_kv_heads,
                       self.head_dim, cache.page_size, cache.num_pages, int(self.window or 0), self.scale, rope=rope,
-                      **({"chunk": self.chunk, "sink": self.sink} if self.chunk or self.sink else {}))
-        return ops.linear(out, self.w_o, meta=ctx.meta)
+                      **({"chunk": self.chunk, "sink": self.sinks if self.learned_sink else self.sink} if self.chunk or self.sink else {}),
+                      **scores)
+        y = ops.linear(out, self.w_o, meta=ctx.meta)
+        return PendingSum((y,), vector=self.b_o) if self.out_bias else y
 
 
 register_part("mixer", "attention", Attention)

@@ -168,7 +168,9 @@ def attention_conv(m, w, pre, hs, eps, shared):
     """The convolved kind: short convolution on q, k, v, norm over the whole projection, sink, value mixing, a gate per head."""
     T = hs.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q, k, v = (causal_conv(hs @ t64(w[pre + n]).T, w[pre + n + ".conv"]) for n in ("q", "k", "v"))
+    q, k, v = (hs @ t64(w[pre + n]).T for n in ("q", "k", "v"))
+    if m.get("conv", 0) > 1:
+        q, k, v = (causal_conv(u, w[pre + n + ".conv"]) for u, n in ((q, "q"), (k, "k"), (v, "v")))
     q = (rms(q, eps) * t64(w[pre + "q.norm"])).view(T, H, d)
     k = (rms(k, eps) * t64(w[pre + "k.norm"])).view(T, G, d)
     v = _value_mix(m, w, pre, v.view(T, G, dv), shared)
@@ -213,9 +215,20 @@ def route(z, top):
     return idx, torch.softmax(val, -1)
 
 
-def moe_ff(f, w, pre, h):
+def route_margin(z, top):
+    """Per row: how far the last chosen logit leads the first one that is not chosen, relative to the largest |logit|
+    (infinite when every expert is chosen): a small lead is a close call that any rounding may turn."""
+    if top >= z.shape[-1]:
+        return torch.full(z.shape[:-1], math.inf, dtype=F)
+    val = torch.topk(z, top + 1, dim=-1).values
+    return (val[..., top - 1] - val[..., top]) / z.abs().max(-1).values
+
+
+def moe_ff(f, w, pre, h, margins=None):
     z = h @ t64(w[pre + "router"]).T + t64(w[pre + "router.b"])
     idx, wt = route(z, f["router"]["top"])
+    if margins is not None:
+        margins.append(route_margin(z, f["router"]["top"]))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for c in range(idx.shape[1]):
@@ -226,7 +239,9 @@ def moe_ff(f, w, pre, h):
 
 
 # ---------------------------------------------------------------------------------------------- the model
-def forward(cfg, w, tokens, layers_out=None):
+def forward(cfg, w, tokens, layers_out=None, margins=None):
+    """``layers_out``: a list that receives the stream after every layer; ``margins``: a list that receives every routed
+    layer's ``route_margin`` per position."""
     eps = cfg["norm"]["eps"]
     x = t64(w["embed"])[torch.as_tensor(tokens, dtype=torch.long)]
     shared = {}
@@ -247,7 +262,7 @@ def forward(cfg, w, tokens, layers_out=None):
         f = ly.get("mlp")
         if f is not None:
             h2 = norm_one_plus(x, w[p + "norm2"], eps)
-            y = dense_ff(f, w, p + "mlp.", h2) if f["kind"] == "dense" else moe_ff(f, w, p + "mlp.", h2)
+            y = dense_ff(f, w, p + "mlp.", h2) if f["kind"] == "dense" else moe_ff(f, w, p + "mlp.", h2, margins)
             x = x + norm_one_plus(gated(y, h2, w[p + "rg2"], w[p + "rg2.b"]), w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
