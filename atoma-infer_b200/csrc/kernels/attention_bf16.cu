@@ -48,6 +48,10 @@ extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 //    the launch and is zero again after it.
 // Before the dependency wait the kernel only touches what no kernel of the step writes: the
 // step's metadata (block table, positions) and keys and values of earlier steps.
+// tanh(x) = 1 - 2 / (exp(2x) + 1) with the fast exponential and division (float32; absolute error of a few 1e-7, against
+// scores whose operands are bfloat16)
+__device__ __forceinline__ float tanh_fast(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+
 // SCORES: the instantiation for capped scores, a bias by distance and a window that keeps the first keep_first keys (see
 // attn_prefill_kernel); the kept keys are tiles of the first split, ahead of its share of the window; `scale_log2` is
 // then the plain scale.
@@ -260,6 +264,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
 
+    // the two rows of the score tile that this lane holds: whether they are heads of the group, and their slopes in base 2
+    const bool row_lo = (lane >> 2) < G, row_hi = (lane >> 2) + 8 < G;
+    const float inv_cap = SCORES && softcap > 0.f ? 1.f / softcap : 0.f;
+    const float slope_lo = SCORES && slopes && row_lo ? slopes[kvh * G + (lane >> 2)] * LOG2E : 0.f;
+    const float slope_hi = SCORES && slopes && row_hi ? slopes[kvh * G + (lane >> 2) + 8] * LOG2E : 0.f;
     for (int t = warp, it = 0; t < ntiles; t += DEC_WARPS, ++it) {
         int stage = 0;
         if (DEC_STAGES == 2) {
@@ -300,12 +309,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
             for (int c = 0; c < 4; ++c) {
                 int key = k0 + n * 8 + (lane & 3) * 2 + (c & 1);
                 if constexpr (SCORES) {
+                    // row (lane >> 2) + 8 (c >> 1) of the tile is that head of the group; rows beyond the group are padding
                     float v = s[n][c] * scale_log2;
-                    if (softcap > 0.f) v = softcap * tanhf(v / softcap);
-                    // row (lane >> 2) + 8 (c >> 1) of the tile is that head of the group
-                    const int r = (lane >> 2) + 8 * (c >> 1);
-                    const float sl = slopes && r < G ? slopes[kvh * G + r] * LOG2E : 0.f;
-                    s[n][c] = key < k1 ? v * LOG2E - sl * (float)(newest - key) : -INFINITY;
+                    if (softcap > 0.f && (c < 2 ? row_lo : row_hi)) v = softcap * tanh_fast(v * inv_cap);
+                    s[n][c] = key < k1 ? v * LOG2E - (c < 2 ? slope_lo : slope_hi) * (float)(newest - key) : -INFINITY;
                 } else {
                     s[n][c] = key < k1 ? s[n][c] * scale_log2 : -INFINITY;
                 }
@@ -587,6 +594,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     // with chunks: below this key some row of the warp sees nothing although the key is not after it
     const int warp_cmax = chunk > 0 && warp_pmax >= 0 ? warp_pmax - warp_pmax % chunk : 0;
     const bool has_padding = warp_last_tok_all >= nt;
+    const float inv_cap = SCORES && softcap > 0.f ? 1.f / softcap : 0.f;
     float slope2[PF_MT][2];  // the rows' slopes, in base 2
     if constexpr (SCORES) {
 #pragma unroll
@@ -666,10 +674,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
                         const int p = prow[mt][c >> 1];
                         if constexpr (SCORES) {
                             // a tile of kept keys holds nothing else; a tile of the window nothing before the window's start
-                            vis = key <= p && (window <= 0 || p - key < window || key < keep_first) &&
-                                  (chunk <= 0 || key >= p - p % chunk) && (kept_tile ? key < kept : (kept <= 0 || key >= kbeg));
+                            if (need_mask || kept_tile)
+                                vis = key <= p && (window <= 0 || p - key < window || key < keep_first) &&
+                                      (chunk <= 0 || key >= p - p % chunk) && (kept_tile ? key < kept : (kept <= 0 || key >= kbeg));
                             float v = s[mt][n][c] * scale_log2;
-                            if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+                            if (softcap > 0.f) v = softcap * tanh_fast(v * inv_cap);
                             s[mt][n][c] = vis ? v * LOG2E - slope2[mt][c >> 1] * (float)(p - key) : -INFINITY;
                         } else {
                             if (need_mask) vis = key <= p && (window <= 0 || p - key < window) && (chunk <= 0 || key >= p - p % chunk);

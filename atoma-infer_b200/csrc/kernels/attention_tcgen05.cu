@@ -187,8 +187,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                        CacheLayout L, const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                        const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, int chunk_arg, int sink_arg,
                        const float* __restrict__ sink_values, float scale_log2, int num_pages, int bt_cap,
-                       int* __restrict__ status) {
+                       float softcap_arg, const float* __restrict__ slopes_arg, int* __restrict__ status) {
     const int chunk = CS ? chunk_arg : 0, sink = CS ? sink_arg : 0;
+    // capped scores (s <- softcap * tanh(s / softcap)) and a bias by distance (slopes[h] * (query position - key position)
+    // taken off): the scores are then turned into their final form, in base 2, before the maximum is taken
+    const float softcap = CS ? softcap_arg : 0.f;
+    const float* slopes = CS ? slopes_arg : nullptr;
+    const bool scored = CS && (softcap > 0.f || slopes != nullptr);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int STAGE = HALVES * HALF_BYTES;  // one K or V tile: 128 rows of the head
@@ -370,6 +375,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         // maximum and base start there, and one of the row's two threads starts its sum with the sink's term
         float m_run = sink ? (CS && sink_values ? sink_values[kvh * G + my_hd] * LOG2E : 0.f) : -INFINITY, m_base = m_run,
               l_run = sink && half == 0 ? 1.f : 0.f;
+        const float slope2 = scored && slopes ? slopes[kvh * G + my_hd] * LOG2E : 0.f;
+        const float plain_scale = scale_log2 * (1.f / LOG2E), inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+        const float sl2 = scored ? 1.f : scale_log2;  // what the scores in v still have to be multiplied by
         // the first key my row sees: its window's or its chunk's start
         int my_lo = window > 0 ? my_pos - window + 1 : 0;
         if (chunk > 0 && my_pos >= 0) my_lo = max(my_lo, my_pos - my_pos % chunk);
@@ -399,6 +407,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                     v[i] = vis ? v[i] : -INFINITY;
                 }
             }
+            if (CS && scored) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    float x = v[i] * plain_scale;
+                    if (softcap > 0.f) x = softcap * (1.f - __fdividef(2.f, __expf(2.f * x * inv_cap) + 1.f));  // tanh, a few 1e-7 absolute
+                    x = fmaf(x, LOG2E, -slope2 * (float)(my_pos - (k0 + half * 64 + i)));
+                    v[i] = v[i] == -INFINITY ? -INFINITY : x;
+                }
+            }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
@@ -407,7 +424,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             float* slot = row_max + (t & 1) * 2 * BQ;  // two sets, so that a fast pair cannot overwrite a slow reader's value
             slot[half * BQ + row] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
-            const float mx = fmaxf(slot[row], slot[BQ + row]) * scale_log2;  // scale > 0: the max commutes with it
+            const float mx = fmaxf(slot[row], slot[BQ + row]) * sl2;  // scale > 0: the max commutes with it
             m_run = fmaxf(m_run, mx);
             // The base moves only when the maximum has outgrown it by more than RESCALE_STEP (or at the first key
             // the row sees): both threads of a row decide alike, they hold the same numbers.
@@ -419,8 +436,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             uint32_t pk[32];  // my 64 keys of P, two to a column
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                float p0 = fast_exp2(fmaf(v[2 * i], scale_log2, -base));
-                float p1 = fast_exp2(fmaf(v[2 * i + 1], scale_log2, -base));
+                float p0 = fast_exp2(fmaf(v[2 * i], sl2, -base));
+                float p1 = fast_exp2(fmaf(v[2 * i + 1], sl2, -base));
                 __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);  // .x = p0 in the low half: the lower key
                 sum4[i & 3] += p0 + p1;
                 pk[i] = *reinterpret_cast<uint32_t*>(&two);
@@ -528,10 +545,27 @@ extern "C" int attn_prefill_tc_supports(int page_size, int nq, int nkv) {
 }
 
 // sink_values (one float per query head, or null): the sink's score per head instead of 0.
+extern "C" int attn_prefill_tc_scores(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                      const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq,
+                                      int nkv, int page_size, int num_pages, int window, int chunk, int sink,
+                                      const float* sink_values, float scale, int max_context, float softcap, const float* slopes,
+                                      int* status, cudaStream_t stream);
+
 extern "C" int attn_prefill_tc_sinks(const void* q, int q_stride, const void* cache, const int* meta, int group,
                                      const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq,
                                      int nkv, int page_size, int num_pages, int window, int chunk, int sink,
                                      const float* sink_values, float scale, int max_context, int* status, cudaStream_t stream) {
+    return attn_prefill_tc_scores(q, q_stride, cache, meta, group, cu_tokens, ctx_lens, out, S, max_q_len, nq, nkv, page_size,
+                                  num_pages, window, chunk, sink, sink_values, scale, max_context, 0.f, nullptr, status, stream);
+}
+
+// softcap > 0: a score s becomes softcap * tanh(s / softcap); slopes (one float per query head, or null): slopes[h] * (query
+// position - key position) is taken off the score.  (A window that keeps first keys is the mma.sync kernel's.)
+extern "C" int attn_prefill_tc_scores(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                      const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq,
+                                      int nkv, int page_size, int num_pages, int window, int chunk, int sink,
+                                      const float* sink_values, float scale, int max_context, float softcap, const float* slopes,
+                                      int* status, cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0) return 0;
     if (!attn_prefill_tc_supports(page_size, nq, nkv)) return (int)cudaErrorInvalidValue;
     EncodeTiledFn fn = encode_fn();
@@ -553,7 +587,7 @@ extern "C" int attn_prefill_tc_sinks(const void* q, int q_stride, const void* ca
     int bt_cap = span / page_size + 2 + BKV / page_size;
     size_t smem = TC_SMEM_FIXED + (size_t)bt_cap * sizeof(int);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
-    const bool cs = chunk > 0 || sink;
+    const bool cs = chunk > 0 || sink || softcap > 0.f || slopes != nullptr;
     static size_t configured[2] = {0, 0};
     if (smem > configured[cs]) {
         cudaError_t err = cs ? cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
@@ -565,11 +599,11 @@ extern "C" int attn_prefill_tc_sinks(const void* q, int q_stride, const void* ca
     if (cs)
         attn_prefill_tc_kernel<true><<<grid, TC_THREADS, smem, stream>>>(map, (const bf16*)q, q_stride, L, meta, group, cu_tokens,
                                                                   ctx_lens, (bf16*)out, nq, window, chunk, sink, sink_values,
-                                                                  scale * LOG2E, num_pages, bt_cap, status);
+                                                                  scale * LOG2E, num_pages, bt_cap, softcap, slopes, status);
     else
         attn_prefill_tc_kernel<false><<<grid, TC_THREADS, smem, stream>>>(map, (const bf16*)q, q_stride, L, meta, group, cu_tokens,
                                                                    ctx_lens, (bf16*)out, nq, window, 0, 0, nullptr, scale * LOG2E,
-                                                                   num_pages, bt_cap, status);
+                                                                   num_pages, bt_cap, 0.f, nullptr, status);
     LAUNCH_RETURN();
 }
 

@@ -517,12 +517,14 @@ class CudaOps:
                                                    window, int(chunk), int(bool(sink)), _p(sinks), ctypes.c_float(scale), splits,
                                                    int(cluster), ctx.max_context, *extra, _p(self.status), self._stream()),
                             "attn_decode")
-            elif not scored and self._prefill_tc(d, page_size, nq, nkv) is not None:
+            elif not keep_first and self._prefill_tc(d, page_size, nq, nkv) is not None:
+                # (a window that keeps first keys is the mma.sync kernel's: its kept keys are tiles of their own)
                 tc = self._prefill_tc(d, page_size, nq, nkv)
-                self._check(tc.attn_prefill_tc_sinks(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                                     _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
-                                                     page_size, num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
-                                                     ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
+                self._check(tc.attn_prefill_tc_scores(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                                      _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
+                                                      page_size, num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
+                                                      ctypes.c_float(scale), ctx.max_context, ctypes.c_float(float(softcap)),
+                                                      _p(slopes), _p(self.status), self._stream()),
                             "attn_prefill_tc")
             else:
                 self._check(lib.attn_prefill_scores(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),

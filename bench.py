@@ -11,7 +11,8 @@ fraction of the measured HBM bandwidth.  Prints ONE JSON line.
 
 ``--designs`` instead of the benchmark: prefill and decode throughput of the Dosovik design beside Llama at equal
 layer sizes, and the design's own kernels beside Llama's like kernels with their fractions of the copy bandwidth.
-``--bumolix``: the same for the Bumolix design (attention beside gated linear attention, selective-scan layers), beside
+``--kulivik``: the same for the Kulivik design (windowed, biased and convolved attention, linear attention with constant
+decays, routed experts), beside Llama and Bumolix.  ``--bumolix``: the same for the Bumolix design (attention beside gated linear attention, selective-scan layers), beside
 Llama and Tutezen.  ``--tutezen``: the same for the Tutezen design (state-space and latent-attention layers, routed experts) at Llama's width
 and as many layer runs.
 
@@ -283,6 +284,29 @@ def bumolix_config(size: str, layers: int, vocab: int = 32768, chunk: int = 1024
             "layers": [pair[i % 2] for i in range(layers)]}
 
 
+def kulivik_config(size: str, layers: int, vocab: int = 32768, window: int = 1024):
+    """A Kulivik configuration of the width, heads and feed-forward size of ``size``, its three kinds of layer in turn:
+    rotated attention inside a window of ``window`` that keeps 4 tokens (capped scores, value mixing) with the dense
+    clamped feed-forward; attention with a bias by distance and a query temperature beside linear attention with constant
+    decays (width / 128 heads of 128 key and 128 value channels) with routed experts (a quarter of the dense size each,
+    two of sixteen chosen); attention behind a convolution of 4 taps with a learned sink and a gate per head, with routed
+    experts."""
+    H, I, nq, nkv, d = DESIGN_SIZES[size]
+    sizes = {"heads": nq, "kv_heads": nkv, "dim": d, "vdim": d, "scale": d ** -0.5}
+    gh = H // 128
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": I // 4}}
+    kinds = [
+        {"type": "attention_2", "mixer": dict(sizes, mask={"size": window, "keep_first": 4}, rot={"dims": d, "base": 1000000.0},
+                                              softcap=30.0, v_mix=True), "mlp": {"kind": "dense", "ff": I, "limit": 7.0}},
+        {"type": "parallel", "mixer": {"left": dict(sizes, q_temp={"coef": 0.5, "every": 64}), "left_scale": 0.6, "right_scale": 0.5,
+                                       "right": {"heads": gh, "dim": 128, "vdim": 128,
+                                                 "decay": [1.0 - 0.5 ** (1 + 8 * i / gh) for i in range(gh)]}}, "mlp": moe},
+        {"type": "attention", "mixer": dict(sizes, conv=4, v_mix=True), "mlp": moe},
+    ]
+    return {"architecture": "Kulivik", "vocab": vocab, "width": H, "norm": {"eps": 1e-6}, "logit_scale": 2.0, "logit_softcap": 30.0,
+            "layers": [kinds[i % 3] for i in range(layers)]}
+
+
 def design_comparison(args, other: str = "dosovik") -> int:
     """Prefill (one prompt of 2,048 tokens) and decode (8 requests, 2,048 tokens cached each, captured graphs)
     through the step function for both designs at each size; then single kernels.  Timing: CUDA events, the median
@@ -319,6 +343,9 @@ def design_comparison(args, other: str = "dosovik") -> int:
         if other == "bumolix":  # beside Llama (equal sizes) and Tutezen (the other design with recurrent layers)
             names = ("llama", "tutezen", other)
             pairs = (pairs[0], tutezen_config(size, max(layers - 2, 2)), bumolix_config(size, layers))
+        if other == "kulivik":  # beside Llama (equal sizes) and Bumolix (the closest design: two mixers side by side)
+            names = ("llama", "bumolix", other)
+            pairs = (pairs[0], bumolix_config(size, layers), kulivik_config(size, layers))
         for name, cfg in zip(names, pairs):
             with tempfile.TemporaryDirectory() as d:
                 with open(os.path.join(d, "config.json"), "w") as f:
@@ -362,7 +389,7 @@ def design_comparison(args, other: str = "dosovik") -> int:
             print(json.dumps(row), flush=True)
             del lm
             torch.cuda.empty_cache()
-    kernels = {"tutezen": tutezen_kernels, "bumolix": bumolix_kernels}.get(other, design_kernels)
+    kernels = {"tutezen": tutezen_kernels, "bumolix": bumolix_kernels, "kulivik": kulivik_kernels}.get(other, design_kernels)
     kernels(make_runtime("bfloat16", "cuda:0"), hbm, median_ms)
     return 0
 
@@ -689,6 +716,125 @@ def bumolix_kernels(rt, hbm, median_ms) -> None:
     ops.check_status()
 
 
+def kulivik_kernels(rt, hbm, median_ms) -> None:
+    """The Kulivik layers' own kernels beside the framework's like kernels, alone, at width 2048 (the sizes of
+    ``kulivik_config("w2048-h64", ...)``): microseconds a call and the fraction of the copy bandwidth that the bytes each
+    must move give; for the recurrence and the attention kernels the rate of their arithmetic.  Rows of 16,384 tokens and
+    of 8 tokens (a decode step: the time of a launch inside a graph)."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import kernel_utils as K
+    from atoma_infer_b200.parts.base import PendingSum
+
+    ops, dev, bf = rt.ops, rt.device, torch.bfloat16
+    H, I, taps = 2048, 8192, 4
+    nq, nkv, d = 32, 8, 64
+    kh, kN, kP = 16, 128, 128          # linear attention with constant decays: heads, key channels, value channels
+    gh, gN, gP = 8, 128, 256           # Bumolix's gated linear attention at this width
+    E, top = 16, 2
+    print(f"kernels alone (copy bandwidth {hbm:.0f} GB/s): name, rows, us, bytes moved / time / copy bandwidth, or the rate")
+    for T in (16384, 8):
+        entries = [(0, T)] if T > 64 else [(100 + i, 1) for i in range(T)]
+        S = len(entries)
+        tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 0)
+        ctx, _ = K.make_context(rt, entries, PAGE, tables)
+        rnd = lambda *shape: torch.randn(*shape, device=dev)  # noqa: E731
+        resid, w = rnd(T, H), torch.ones(H, device=dev)
+        a, b, c = (rnd(T, H).to(bf) for _ in range(3))
+        out, out2 = (torch.empty(T, H, device=dev, dtype=bf) for _ in range(2))
+        mu, kept, last = torch.rand(H, device=dev), torch.zeros(S, H, device=dev), torch.empty(S, H, device=dev)
+        gate32, gbias = rnd(T, H), torch.zeros(H, device=dev)
+        qkv = rnd(T, (nq + 2 * nkv) * d).to(bf)
+        cache = torch.zeros(num_pages, 2, nkv, PAGE, d, device=dev, dtype=bf)
+        q_out = torch.empty(T, nq * d, device=dev, dtype=bf)
+        bias, inv_freq = torch.ones((nq + 2 * nkv) * d, device=dev, dtype=bf), torch.ones(d // 2, device=dev)
+        hw = torch.ones(d, device=dev, dtype=bf)
+        att, gate, hgate = rnd(T, nq, d).to(bf), rnd(T, nq, d).to(bf), rnd(T, nq).to(bf)
+        k_proj = (rnd(T, 2 * kh * kN + 2 * kh * kP) * 0.5).to(bf)
+        k_state, k_o = torch.zeros(S, kh, kN, kP, device=dev), torch.empty(T, kh * kP, device=dev)
+        k_dec, k_y, k_w = torch.full((kh,), 0.97, device=dev), torch.empty(T, kh * kP, device=dev, dtype=bf), torch.ones(kh * kP, device=dev)
+        g_proj = (rnd(T, 2 * gh * gN + 2 * gh * gP) * 0.5).to(bf)
+        g_z, g_bias = rnd(T, gh * gN), torch.zeros(gh * gN, device=dev)
+        g_state, g_o = torch.zeros(S, gh, gN, gP, device=dev), torch.empty(T, gh * gP, device=dev)
+        g_y, g_w = torch.empty(T, gh * gP, device=dev, dtype=bf), torch.ones(gP, device=dev)
+        c_w, c_ring = rnd(taps, (nq + 2 * nkv) * d), torch.zeros(S, taps - 1, (nq + 2 * nkv) * d, device=dev)
+        c_out = torch.empty(T, (nq + 2 * nkv) * d, device=dev, dtype=bf)
+        gu, act = rnd(T, 2 * I).to(bf), torch.empty(T, I, device=dev, dtype=bf)
+        x, wr, rb = rnd(T, H).to(bf), rnd(E, H), rnd(E)
+        ids, wts = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, device=dev)
+        twice = 2 if T >= 128 else 1  # (chunks of time run twice)
+        rows_b = T * (nq + 2 * nkv) * d * 2 * 2
+        cases = [
+            ("kulivik: norm + row shifted toward the token before", lambda: ops.norm_shift(resid, w, 1e-6, ctx, shift=mu, state=kept, h=out, hs=out2, last=last),
+             T * H * (4 + 2 + 2), None),
+            ("llama:   add + RMSNorm", lambda: ops.add_rmsnorm(resid, a, w, 1e-5, out, ctx.meta, T), T * H * (4 + 2 + 4 + 2), None),
+            ("kulivik: gate, norm of two weighted terms, sum into the stream + next norm",
+             lambda: ops.gated_norm_add(resid, PendingSum((a, b), 1.0, factors=(0.6, 0.5)), gate32, gbias, w, 1e-6, ctx, next_norm=(w, 1e-6, out), keep=(last, kept)),
+             T * H * (2 * 2 + 4 + 4 + 4 + 2), None),
+            ("bumolix: weighted pending sum of three + two RMSNorms",
+             lambda: ops.sum_rmsnorm(resid, PendingSum((a, b, c), 0.5, factors=(0.5, 1.25, 1.0)), w, 1e-5, out, ctx.meta, T, second=(w, 1e-5, out2)),
+             T * H * (4 + 3 * 2 + 4 + 2 * 2), None),
+            ("kulivik: attention rows (bias, weighted norm per head, interleaved rotation, pages)",
+             lambda: ops.qkv_prepare(qkv, ctx, cache, 0, q_out, nq=nq, nkv=nkv, d=d, dv=d, dp=d, page_size=PAGE, num_pages=num_pages,
+                                     store_kv=True, bias=bias, q_norm=hw, k_norm=hw, eps=1e-6, inv_freq=inv_freq, rot=d, head_norm=True, interleaved=True),
+             rows_b, None),
+            ("kulivik: attention rows (query temperature, pages; no rotation)",
+             lambda: ops.qkv_prepare(qkv, ctx, cache, 0, q_out, nq=nq, nkv=nkv, d=d, dv=d, dp=d, page_size=PAGE, num_pages=num_pages,
+                                     store_kv=True, eps=1e-6, q_temp=(0.5, 64)), rows_b, None),
+            ("bumolix: attention rows (bias, half rotation, norm per head, pages)",
+             lambda: ops.qkv_prepare(qkv, ctx, cache, 0, q_out, nq=nq, nkv=nkv, d=d, dv=d, dp=d, page_size=PAGE, num_pages=num_pages,
+                                     store_kv=True, bias=bias, eps=1e-5, inv_freq=inv_freq[:d // 4], rot=d // 2, head_norm=True), rows_b, None),
+            ("llama:   rotation + pages", lambda: ops.rope_kv_store(qkv, ctx.positions, ctx.token_entry, ctx.meta, 0, inv_freq,
+                                                                    cache, num_pages, T, nq, nkv, d, d, PAGE, True), rows_b, None),
+            ("kulivik: convolution of 4 taps on q, k, v (+ ring)",
+             lambda: (ops.causal_conv_act(qkv, c_w, None, c_ring, ctx, c_out, act="none") or ops.causal_conv_save(qkv, c_ring, ctx, taps)),
+             rows_b, None),
+            ("kulivik: one gate per head (sigmoid, in place)", lambda: ops.head_gate(att, hgate, ctx.meta), T * nq * d * 2 * 2, None),
+            ("bumolix: output gate (sigmoid, in place)", lambda: ops.sigmoid_gate(att, gate, ctx.meta), T * nq * d * 2 * 3, None),
+            ("kulivik: linear attention, constant decays, SiLU, 16 x 128 x 128 (float32 FMA)",
+             lambda: ops.gla_scan(k_proj[:, :kh * kN], k_proj[:, kh * kN:2 * kh * kN], k_proj[:, 2 * kh * kN:2 * kh * kN + kh * kP], None, None,
+                                  1.0, 1.0, k_state, ctx, k_o, heads=kh, dim=kN, vdim=kP, head_decay=k_dec, silu=True),
+             T * (2 * kh * kN * 2 + kh * kP * 2 + kh * kP * 4) + 2 * S * kh * kN * kP * 4, 6.0 * T * kh * kN * kP * twice),
+            ("bumolix: gated linear attention, 8 x 128 x 256 (float32 FMA)",
+             lambda: ops.gla_scan(g_proj[:, :gh * gN], g_proj[:, gh * gN:2 * gh * gN], g_proj[:, 2 * gh * gN:2 * gh * gN + gh * gP], g_z, g_bias,
+                                  8.0, gN ** -0.5, g_state, ctx, g_o, heads=gh, dim=gN, vdim=gP),
+             T * (2 * gh * gN * 2 + gh * gP * 2 + gh * gN * 4 + gh * gP * 4) + 2 * S * gh * gN * gP * 4, 6.0 * T * gh * gN * gP * twice),
+            ("kulivik: norm over the whole row, weight, sigmoid gate", lambda: ops.row_norm_gate(k_o, k_proj[:, 2 * kh * kN + kh * kP:], k_w, 1e-6, k_y, ctx.meta),
+             T * kh * kP * (4 + 2 + 2), None),
+            ("bumolix: norm per head, shared weight, SiLU gate", lambda: ops.head_norm_gate(g_o, g_proj[:, 2 * gh * gN + gh * gP:], g_w, 1e-5, g_y, ctx.meta, gh),
+             T * gh * gP * (4 + 2 + 2), None),
+            ("kulivik: clamped gated activation", lambda: ops.clamped_glu(gu, act, 7.0, 1.702, ctx.meta), T * I * 2 * 3, None),
+            ("llama:   SiLU * up", lambda: ops.silu_mul(gu, act, ctx.meta, T, I), T * I * 2 * 3, None),
+            ("kulivik: router (bias, weights over the chosen)", lambda: ops.moe_route(x, wr, ids, wts, ctx.meta, bias=rb, over_chosen=True), T * H * 2, None),
+            ("tutezen: router", lambda: ops.moe_route(x, wr, ids, wts, ctx.meta), T * H * 2, None),
+        ]
+        for name, fn, nbytes, flops in cases:
+            us = _graph_us(fn, n=16 if T <= 64 else 2)
+            rate = f"  {flops / (us * 1e-6) / 1e12:7.1f} TFLOP/s" if flops else ""
+            print(f"  {name:84s} {T:5d} rows {us:9.1f} us  {nbytes / (us * 1e-6) / (hbm * 1e9):5.2f}{rate}")
+        # attention: a prompt of T tokens (or T decode tokens over 2,048 cached ones)
+        entries = [(0, T)] if T > 64 else [(2047, 1)] * T
+        tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 1)
+        ctx, _ = K.make_context(rt, entries, PAGE, tables)
+        cache = torch.randn(num_pages, 2, nkv, PAGE, d, device=dev).to(bf)
+        q, o = torch.randn(T, nq * d, device=dev).to(bf), torch.empty(T, nq * d, device=dev, dtype=bf)
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / nq) for h in range(nq)], device=dev)
+        sinks = torch.zeros(nq, device=dev)
+        for name, window, kw in (("llama:   attention, 32 x 64 over 8 x 64, all keys", 0, {}), ("llama:   attention, window 1024", 1024, {}),
+                                 ("bumolix: attention, chunks of 1024 + sink", 0, {"chunk": 1024, "sink": True}),
+                                 ("kulivik: attention, window 1024 that keeps 4, capped scores", 1024, {"keep_first": 4, "softcap": 30.0}),
+                                 ("kulivik: attention, window 1024 that keeps 4", 1024, {"keep_first": 4}),
+                                 ("kulivik: attention, all keys, bias by distance", 0, {"slopes": slopes}),
+                                 ("kulivik: attention, all keys, learned sink", 0, {"sink": sinks})):
+            us = _graph_us(lambda: ops.attention(q, nq * d, cache, ctx, 0, o, nq, nkv, d, PAGE, num_pages, window, 0.125, **kw), n=4)
+            chunk = kw.get("chunk", 0)
+            keys = (min(chunk, T) / 2 if chunk else (min(window, T) if window and T > window else T / 2)) if T > 64 else min(window or chunk or 2048, 2048)
+            flops = 4.0 * T * nq * d * keys
+            print(f"  {name:84s} {T:5d} rows {us:9.1f} us         {flops / (us * 1e-6) / 1e12:7.1f} TFLOP/s")
+    ops.check_status()
+
+
 def layer_kernel_phases(eng, args, prompt, greedy, cfg) -> int:
     """Decode steps through the persistent layer kernel (csrc/kernels/decode_stack.cu), eagerly, with every block
     writing the global clock after each phase and each barrier of each layer; prints the mean, the slowest and the
@@ -799,6 +945,8 @@ def main() -> int:
     ap.add_argument("--tutezen", action="store_true",
                     help="instead of the benchmark: prefill and decode throughput of the Tutezen design beside Llama at equal "
                          "width and as many layer runs (a JSON line each), then the design's kernels alone beside like kernels")
+    ap.add_argument("--kulivik", action="store_true",
+                    help="the Kulivik design beside Llama and Bumolix at equal layer sizes through the step function, then its kernels alone")
     ap.add_argument("--bumolix", action="store_true",
                     help="instead of the benchmark: prefill and decode throughput of the Bumolix design beside Llama and Tutezen "
                          "at equal width and as many layer runs (a JSON line each), then the design's kernels alone beside like kernels")
@@ -824,6 +972,8 @@ def main() -> int:
         return design_comparison(args, other="tutezen")
     if args.bumolix:
         return design_comparison(args, other="bumolix")
+    if args.kulivik:
+        return design_comparison(args, other="kulivik")
     if args.model != "1b":
         return serving_workload(args.model)
 

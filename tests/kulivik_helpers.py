@@ -164,3 +164,12 @@ def want_before(steps, limit: Dict[str, int], strip: int = 1):
             pos[e["id"]] = start + len(e["tokens"])
         out.append(dict(s, entries=entries))
     return out
+
+
+def rounding_errors(model_dir: str, cfg: dict, seqs: Dict[str, List[int]], ref: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """Per position, how far the plain implementation itself moves (largest logit difference over the largest logit of
+    the sequence) when what its matrix products read and write is rounded to bfloat16: the measure of how much a
+    position amplifies roundings that no implementation in that type can avoid."""
+    w = helpers.read_weights(model_dir)
+    return {k: (PK.forward(cfg, w, v, round_to=torch.bfloat16) - ref[k]).abs().max(-1).values / ref[k].abs().max()
+            for k, v in seqs.items()}

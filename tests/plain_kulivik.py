@@ -17,8 +17,18 @@ import torch
 F = torch.float64
 
 
+_ROUND = None  # a storage type that matrix products read and write through (None: exact), see ``forward``
+
+
 def t64(x):
     return x.to(F)
+
+
+def lin(x, w):
+    """x W^T; with a storage type set, what the product reads and what it writes is rounded to that type first."""
+    if _ROUND is None:
+        return x @ t64(w).T
+    return (x.to(_ROUND).to(F) @ t64(w).T).to(_ROUND).to(F)
 
 
 def rms(x, eps):
@@ -37,7 +47,7 @@ def token_shift(h, mu):
 
 
 def gated(result, h, wg, bg):
-    return result * torch.sigmoid(h @ t64(wg).T + t64(bg))
+    return result * torch.sigmoid(lin(h, wg) + t64(bg))
 
 
 def gelu_tanh(z):
@@ -140,9 +150,9 @@ def attention_rotary(m, w, pre, hs, eps, shared):
     kept first tokens, value mixing."""
     T = hs.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (hs @ t64(w[pre + "q"]).T + t64(w[pre + "q.b"])).view(T, H, d)
-    k = (hs @ t64(w[pre + "k"]).T + t64(w[pre + "k.b"])).view(T, G, d)
-    v = (hs @ t64(w[pre + "v"]).T + t64(w[pre + "v.b"])).view(T, G, dv)
+    q = (lin(hs, w[pre + "q"]) + t64(w[pre + "q.b"])).view(T, H, d)
+    k = (lin(hs, w[pre + "k"]) + t64(w[pre + "k.b"])).view(T, G, d)
+    v = (lin(hs, w[pre + "v"]) + t64(w[pre + "v.b"])).view(T, G, dv)
     q = rms(q, eps) * t64(w[pre + "q.norm"])
     k = rms(k, eps) * t64(w[pre + "k.norm"])
     rot = m.get("rot")
@@ -152,7 +162,7 @@ def attention_rotary(m, w, pre, hs, eps, shared):
     mask = m.get("mask")
     see = visible(T, mask["size"], mask.get("keep_first", 0)) if mask else visible(T)
     o = softmax_attention(q, k, v, m["scale"], see, softcap=m.get("softcap"))
-    return o.reshape(T, H * dv) @ t64(w[pre + "o"]).T + t64(w[pre + "o.b"])
+    return lin(o.reshape(T, H * dv), w[pre + "o"]) + t64(w[pre + "o.b"])
 
 
 def _value_mix(m, w, pre, v, shared):
@@ -168,45 +178,46 @@ def attention_conv(m, w, pre, hs, eps, shared):
     """The convolved kind: short convolution on q, k, v, norm over the whole projection, sink, value mixing, a gate per head."""
     T = hs.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q, k, v = (hs @ t64(w[pre + n]).T for n in ("q", "k", "v"))
+    q, k, v = (lin(hs, w[pre + n]) for n in ("q", "k", "v"))
     if m.get("conv", 0) > 1:
         q, k, v = (causal_conv(u, w[pre + n + ".conv"]) for u, n in ((q, "q"), (k, "k"), (v, "v")))
     q = (rms(q, eps) * t64(w[pre + "q.norm"])).view(T, H, d)
     k = (rms(k, eps) * t64(w[pre + "k.norm"])).view(T, G, d)
     v = _value_mix(m, w, pre, v.view(T, G, dv), shared)
     o = softmax_attention(q, k, v, m["scale"], visible(T), sink=t64(w[pre + "sink"]))
-    o = o * torch.sigmoid(hs @ t64(w[pre + "g"]).T)[:, :, None]
-    return o.reshape(T, H * dv) @ t64(w[pre + "o"]).T
+    o = o * torch.sigmoid(lin(hs, w[pre + "g"]))[:, :, None]
+    return lin(o.reshape(T, H * dv), w[pre + "o"])
 
 
 def side_by_side(m, w, pre, hs, eps):
     T = hs.shape[0]
     a, pl = m["left"], pre + "left."
     H, G, d, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
-    q = (hs @ t64(w[pl + "q"]).T).view(T, H, d)
-    k = (hs @ t64(w[pl + "k"]).T).view(T, G, d)
-    v = (hs @ t64(w[pl + "v"]).T).view(T, G, dv)
+    q = (lin(hs, w[pl + "q"])).view(T, H, d)
+    k = (lin(hs, w[pl + "k"])).view(T, G, d)
+    v = (lin(hs, w[pl + "v"])).view(T, G, dv)
     qt = a.get("q_temp")
     if qt:
         q = q * query_temperature(T, qt["coef"], qt["every"])[:, None, None]
-    left = softmax_attention(q, k, v, a["scale"], visible(T), slopes=slopes_of(H)).reshape(T, H * dv) @ t64(w[pl + "o"]).T
+    left = softmax_attention(q, k, v, a["scale"], visible(T), slopes=slopes_of(H)).reshape(T, H * dv)
+    left = lin(left, w[pl + "o"])
     r, pr = m["right"], pre + "right."
     H2, n, p = r["heads"], r["dim"], r["vdim"]
-    q2 = silu(hs @ t64(w[pr + "q"]).T).view(T, H2, n)
-    k2 = silu(hs @ t64(w[pr + "k"]).T).view(T, H2, n)
-    v2 = silu(hs @ t64(w[pr + "v"]).T).view(T, H2, p)
+    q2 = silu(lin(hs, w[pr + "q"])).view(T, H2, n)
+    k2 = silu(lin(hs, w[pr + "k"])).view(T, H2, n)
+    v2 = silu(lin(hs, w[pr + "v"])).view(T, H2, p)
     o2 = decaying_state(q2, k2, v2, r["decay"]).reshape(T, H2 * p)
-    o2 = rms(o2, eps) * t64(w[pr + "norm"]) * torch.sigmoid(hs @ t64(w[pr + "g"]).T)
-    right = o2 @ t64(w[pr + "o"]).T
+    o2 = rms(o2, eps) * t64(w[pr + "norm"]) * torch.sigmoid(lin(hs, w[pr + "g"]))
+    right = lin(o2, w[pr + "o"])
     return m["left_scale"] * left + m["right_scale"] * right
 
 
 # ---------------------------------------------------------------------------------------------- feed-forwards
 def dense_ff(f, w, pre, h):
     lim = f["limit"]
-    g = torch.clamp(h @ t64(w[pre + "gate"]).T, max=lim)
-    u = torch.clamp(h @ t64(w[pre + "up"]).T, -lim, lim)
-    return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ t64(w[pre + "down"]).T
+    g = torch.clamp(lin(h, w[pre + "gate"]), max=lim)
+    u = torch.clamp(lin(h, w[pre + "up"]), -lim, lim)
+    return lin(g * torch.sigmoid(1.702 * g) * (u + 1.0), w[pre + "down"])
 
 
 def route(z, top):
@@ -225,7 +236,7 @@ def route_margin(z, top):
 
 
 def moe_ff(f, w, pre, h, margins=None):
-    z = h @ t64(w[pre + "router"]).T + t64(w[pre + "router.b"])
+    z = lin(h, w[pre + "router"]) + t64(w[pre + "router.b"])
     idx, wt = route(z, f["router"]["top"])
     if margins is not None:
         margins.append(route_margin(z, f["router"]["top"]))
@@ -233,15 +244,25 @@ def moe_ff(f, w, pre, h, margins=None):
     for t in range(h.shape[0]):
         for c in range(idx.shape[1]):
             e = pre + f"e{int(idx[t, c])}."
-            y = silu(h[t] @ t64(w[e + "gate"]).T) * (h[t] @ t64(w[e + "up"]).T)
-            out[t] = out[t] + wt[t, c] * (y @ t64(w[e + "down"]).T)
+            y = silu(lin(h[t], w[e + "gate"])) * (lin(h[t], w[e + "up"]))
+            out[t] = out[t] + wt[t, c] * (lin(y, w[e + "down"]))
     return out
 
 
 # ---------------------------------------------------------------------------------------------- the model
-def forward(cfg, w, tokens, layers_out=None, margins=None):
+def forward(cfg, w, tokens, layers_out=None, margins=None, round_to=None):
     """``layers_out``: a list that receives the stream after every layer; ``margins``: a list that receives every routed
-    layer's ``route_margin`` per position."""
+    layer's ``route_margin`` per position; ``round_to``: a storage type through which every matrix product reads and
+    writes (to see how far rounding alone moves a position)."""
+    global _ROUND
+    _ROUND = round_to
+    try:
+        return _forward(cfg, w, tokens, layers_out, margins)
+    finally:
+        _ROUND = None
+
+
+def _forward(cfg, w, tokens, layers_out, margins):
     eps = cfg["norm"]["eps"]
     x = t64(w["embed"])[torch.as_tensor(tokens, dtype=torch.long)]
     shared = {}
@@ -267,6 +288,6 @@ def forward(cfg, w, tokens, layers_out=None, margins=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     h = norm_one_plus(x, w["final.norm"], eps)
-    z = (h @ t64(w["embed"]).T) * cfg.get("logit_scale", 1.0)
+    z = (lin(h, w["embed"])) * cfg.get("logit_scale", 1.0)
     cap = cfg.get("logit_softcap")
     return cap * torch.tanh(z / cap) if cap else z
