@@ -408,12 +408,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                 }
             }
             if (CS && scored) {
+                // - slope (my_pos - key) = c0 + slope i for key = k0 + 64 half + i: two multiply-adds a score, no conversion
+                const float c0 = -slope2 * (float)(my_pos - (k0 + half * 64));
+                if (softcap > 0.f) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    float x = v[i] * plain_scale;
-                    if (softcap > 0.f) x = softcap * (1.f - __fdividef(2.f, __expf(2.f * x * inv_cap) + 1.f));  // tanh, a few 1e-7 absolute
-                    x = fmaf(x, LOG2E, -slope2 * (float)(my_pos - (k0 + half * 64 + i)));
-                    v[i] = v[i] == -INFINITY ? -INFINITY : x;
+                    for (int i = 0; i < 64; ++i) {
+                        float x = v[i] * plain_scale;
+                        x = softcap * (1.f - __fdividef(2.f, __expf(2.f * x * inv_cap) + 1.f));  // tanh, a few 1e-7 absolute
+                        x = fmaf(x, LOG2E, fmaf(slope2, (float)i, c0));
+                        v[i] = v[i] == -INFINITY ? -INFINITY : x;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) v[i] = fmaf(v[i], scale_log2, fmaf(slope2, (float)i, c0));  // (a hidden key stays at -inf)
                 }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
