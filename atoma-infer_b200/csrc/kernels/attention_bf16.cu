@@ -663,6 +663,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
             }
             // only tiles that cross a row's last visible key (or a window's edge, or the range's ends) need a mask
             const bool need_mask = has_padding || window > 0 || k0 + PF_KT - 1 > warp_pmin || k0 < kbeg || k0 < warp_cmax;
+            // a tile that every row of the warp sees whole: inside the window of the warp's last row and not after its first
+            // row, or kept keys only (all of them lie before every row's window)
+            const bool all_seen = SCORES && !has_padding && chunk <= 0 &&
+                                  (kept_tile ? k0 + PF_KT <= kept
+                                             : (k0 >= kbeg && k0 + PF_KT - 1 <= warp_pmin && (window <= 0 || k0 >= warp_pmax - window + 1)));
 #pragma unroll
             for (int mt = 0; mt < PF_MT; ++mt) {
 #pragma unroll
@@ -674,7 +679,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
                         const int p = prow[mt][c >> 1];
                         if constexpr (SCORES) {
                             // a tile of kept keys holds nothing else; a tile of the window nothing before the window's start
-                            if (need_mask || kept_tile)
+                            if ((need_mask || kept_tile) && !all_seen)
                                 vis = key <= p && (window <= 0 || p - key < window || key < keep_first) &&
                                       (chunk <= 0 || key >= p - p % chunk) && (kept_tile ? key < kept : (kept <= 0 || key >= kbeg));
                             float v = s[mt][n][c] * scale_log2;
