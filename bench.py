@@ -286,7 +286,7 @@ def bumolix_config(size: str, layers: int, vocab: int = 32768, chunk: int = 1024
 
 def kulivik_config(size: str, layers: int, vocab: int = 32768, window: int = 1024):
     """A Kulivik configuration of the width, heads and feed-forward size of ``size``, its three kinds of layer in turn:
-    rotated attention inside a window of ``window`` that keeps 4 tokens (capped scores, value mixing) with the dense
+    rotated attention inside a window of ``window`` that keeps 8 tokens (capped scores, value mixing) with the dense
     clamped feed-forward; attention with a bias by distance and a query temperature beside linear attention with constant
     decays (width / 128 heads of 128 key and 128 value channels) with routed experts (a quarter of the dense size each,
     two of sixteen chosen); attention behind a convolution of 4 taps with a learned sink and a gate per head, with routed
@@ -296,14 +296,14 @@ def kulivik_config(size: str, layers: int, vocab: int = 32768, window: int = 102
     gh = H // 128
     moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": I // 4}}
     kinds = [
-        {"type": "attention_2", "mixer": dict(sizes, mask={"size": window, "keep_first": 4}, rot={"dims": d, "base": 1000000.0},
-                                              softcap=30.0, v_mix=True), "mlp": {"kind": "dense", "ff": I, "limit": 7.0}},
-        {"type": "parallel", "mixer": {"left": dict(sizes, q_temp={"coef": 0.5, "every": 64}), "left_scale": 0.6, "right_scale": 0.5,
+        {"type": "attention_2", "mixer": dict(sizes, mask={"size": window, "keep_first": 8}, rot={"dims": d, "base": 500000.0},
+                                              softcap=50.0, v_mix=True), "mlp": {"kind": "dense", "ff": I, "limit": 7.0}},
+        {"type": "parallel", "mixer": {"left": dict(sizes, q_temp={"coef": 0.25, "every": 128}), "left_scale": 0.7, "right_scale": 0.4,
                                        "right": {"heads": gh, "dim": 128, "vdim": 128,
                                                  "decay": [1.0 - 0.5 ** (1 + 8 * i / gh) for i in range(gh)]}}, "mlp": moe},
         {"type": "attention", "mixer": dict(sizes, conv=4, v_mix=True), "mlp": moe},
     ]
-    return {"architecture": "Kulivik", "vocab": vocab, "width": H, "norm": {"eps": 1e-6}, "logit_scale": 2.0, "logit_softcap": 30.0,
+    return {"architecture": "Kulivik", "vocab": vocab, "width": H, "norm": {"eps": 1e-5}, "logit_scale": 1.5, "logit_softcap": 40.0,
             "layers": [kinds[i % 3] for i in range(layers)]}
 
 
@@ -770,7 +770,7 @@ def kulivik_kernels(rt, hbm, median_ms) -> None:
              T * H * (4 + 2 + 2), None),
             ("llama:   add + RMSNorm", lambda: ops.add_rmsnorm(resid, a, w, 1e-5, out, ctx.meta, T), T * H * (4 + 2 + 4 + 2), None),
             ("kulivik: gate, norm of two weighted terms, sum into the stream + next norm",
-             lambda: ops.gated_norm_add(resid, PendingSum((a, b), 1.0, factors=(0.6, 0.5)), gate32, gbias, w, 1e-6, ctx, next_norm=(w, 1e-6, out), keep=(last, kept)),
+             lambda: ops.gated_norm_add(resid, PendingSum((a, b), 1.0, factors=(0.7, 0.4)), gate32, gbias, w, 1e-6, ctx, next_norm=(w, 1e-6, out), keep=(last, kept)),
              T * H * (2 * 2 + 4 + 4 + 4 + 2), None),
             ("bumolix: weighted pending sum of three + two RMSNorms",
              lambda: ops.sum_rmsnorm(resid, PendingSum((a, b, c), 0.5, factors=(0.5, 1.25, 1.0)), w, 1e-5, out, ctx.meta, T, second=(w, 1e-5, out2)),
@@ -781,7 +781,7 @@ def kulivik_kernels(rt, hbm, median_ms) -> None:
              rows_b, None),
             ("kulivik: attention rows (query temperature, pages; no rotation)",
              lambda: ops.qkv_prepare(qkv, ctx, cache, 0, q_out, nq=nq, nkv=nkv, d=d, dv=d, dp=d, page_size=PAGE, num_pages=num_pages,
-                                     store_kv=True, eps=1e-6, q_temp=(0.5, 64)), rows_b, None),
+                                     store_kv=True, eps=1e-6, q_temp=(0.25, 128)), rows_b, None),
             ("bumolix: attention rows (bias, half rotation, norm per head, pages)",
              lambda: ops.qkv_prepare(qkv, ctx, cache, 0, q_out, nq=nq, nkv=nkv, d=d, dv=d, dp=d, page_size=PAGE, num_pages=num_pages,
                                      store_kv=True, bias=bias, eps=1e-5, inv_freq=inv_freq[:d // 4], rot=d // 2, head_norm=True), rows_b, None),
@@ -823,8 +823,8 @@ def kulivik_kernels(rt, hbm, median_ms) -> None:
         sinks = torch.zeros(nq, device=dev)
         for name, window, kw in (("llama:   attention, 32 x 64 over 8 x 64, all keys", 0, {}), ("llama:   attention, window 1024", 1024, {}),
                                  ("bumolix: attention, chunks of 1024 + sink", 0, {"chunk": 1024, "sink": True}),
-                                 ("kulivik: attention, window 1024 that keeps 4, capped scores", 1024, {"keep_first": 4, "softcap": 30.0}),
-                                 ("kulivik: attention, window 1024 that keeps 4", 1024, {"keep_first": 4}),
+                                 ("kulivik: attention, window 1024 that keeps 8, capped scores", 1024, {"keep_first": 8, "softcap": 50.0}),
+                                 ("kulivik: attention, window 1024 that keeps 8", 1024, {"keep_first": 8}),
                                  ("kulivik: attention, all keys, bias by distance", 0, {"slopes": slopes}),
                                  ("kulivik: attention, all keys, learned sink", 0, {"sink": sinks})):
             us = _graph_us(lambda: ops.attention(q, nq * d, cache, ctx, 0, o, nq, nkv, d, PAGE, num_pages, window, 0.125, **kw), n=4)

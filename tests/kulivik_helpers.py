@@ -92,7 +92,7 @@ CONFIGS = {
     # the rotated kind first: no window, no cap, a whole head rotated, no value mixing; one key/value head for eight query
     # heads without a temperature; no convolution; all experts chosen; logits as they are
     "V": (config(128, 300, [layer("attention_2", rotary(4, 2, 32, 48, 0.15, rot=32, base=1e6), moe(24, 3, 3)),
-                            layer("parallel", pair(biased(8, 1, 16, 16, 0.25), decaying(4, 8, 40, (1.0, 0.9, 0.3, 0.999)),
+                            layer("parallel", pair(biased(8, 1, 16, 16, 0.25), decaying(4, 8, 40, (1.0, 0.9, 0.3, 0.995)),
                                                    1.0, 1.0), dense(72, 3.0)),
                             layer("attention", convolved(2, 1, 64, 64, 0.125, v_mix=True), moe(64, 4, 2))], eps=1e-6), 16),
     # sizes that are no multiple of four (heads of 18 with 6 rotated, values of 10); a window of 20 that keeps nothing (its
@@ -102,7 +102,7 @@ CONFIGS = {
                           layer("attention_2", rotary(4, 2, 18, 10, 0.3, window=20, rot=6, base=50.0, softcap=2.0, v_mix=True),
                                 moe(32, 6, 2)),
                           layer("attention", convolved(4, 2, 18, 10, 0.3, conv=2, v_mix=True)),
-                          layer("attention_2", rotary(4, 4, 16, 16, 0.25, window=5, keep_first=7, softcap=30.0), dense(80, 1.5)),
+                          layer("attention_2", rotary(4, 4, 16, 16, 0.25, window=5, keep_first=7, softcap=25.0), dense(80, 1.75)),
                           layer("parallel", pair(biased(6, 3, 16, 16, 0.2), decaying(1, 40, 24, (0.99,)), 0.4, 1.3),
                                 moe(16, 2, 1))], logit_softcap=8.0), 8),
 }

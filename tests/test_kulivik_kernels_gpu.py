@@ -89,7 +89,7 @@ def test_gated_normed_sum_into_the_stream(rts, dtype, H, terms):
     T = 7
     ctx, _ = K.make_context(rt, [(0, 4), (9, 3)], 16, [[1], [2]])
     ts = [torch.randn(T, H, generator=g).to(rt.dtype) for _ in range(terms)]
-    fs = [0.6, 0.5, -1.25][:terms]
+    fs = [0.7, 0.45, -1.25][:terms]
     vec, gate, gb = torch.randn(H, generator=g), 2 * torch.randn(T, H, generator=g), torch.randn(H, generator=g)
     w, w2 = 1 + 0.2 * torch.randn(H, generator=g), 1 + 0.2 * torch.randn(H, generator=g)
     x = torch.randn(T, H, generator=g)
@@ -150,7 +150,7 @@ SCORE_KINDS = {"window+kept+cap": dict(softcap=3.0), "window+kept": dict(), "slo
 
 
 @pytest.mark.parametrize("dtype,fast", [("float32", True), ("bfloat16", True), ("bfloat16", False)])
-@pytest.mark.parametrize("d,nq,nkv,page,window,keep", [(48, 4, 2, 16, 40, 4), (64, 4, 1, 8, 64, 9), (32, 6, 3, 4, 21, 30), (128, 2, 2, 16, 100, 1),
+@pytest.mark.parametrize("d,nq,nkv,page,window,keep", [(48, 6, 2, 16, 36, 5), (64, 4, 1, 8, 64, 9), (32, 6, 3, 4, 21, 30), (128, 2, 2, 16, 100, 1),
                                                         (16, 8, 8, 16, 7, 0), (64, 4, 2, 16, 50, 0)])
 def test_scores_in_prompt_portions(rts, dtype, fast, d, nq, nkv, page, window, keep):
     """Portions that start and end anywhere, beside single tokens; for the last query of each request one key towers: the
@@ -178,7 +178,7 @@ def test_scores_in_prompt_portions(rts, dtype, fast, d, nq, nkv, page, window, k
 
 
 @pytest.mark.parametrize("dtype,fast", [("float32", True), ("bfloat16", True), ("bfloat16", False)])
-@pytest.mark.parametrize("d,nq,nkv,page,window,keep", [(48, 4, 2, 16, 40, 4), (64, 8, 1, 8, 512, 20), (32, 6, 3, 4, 21, 30), (128, 4, 2, 16, 300, 3)])
+@pytest.mark.parametrize("d,nq,nkv,page,window,keep", [(48, 6, 2, 16, 36, 5), (64, 8, 1, 8, 512, 20), (32, 6, 3, 4, 21, 30), (128, 4, 2, 16, 300, 3)])
 def test_scores_in_decode_steps(rts, dtype, fast, d, nq, nkv, page, window, keep):
     """Every request brings one token: at the start of a sequence, while the window still holds everything, when it has
     just begun to pass over the kept tokens' neighbours, and far beyond."""
@@ -200,7 +200,7 @@ def test_scores_in_decode_steps(rts, dtype, fast, d, nq, nkv, page, window, keep
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("entries", [[(0, 5), (13, 3), (40, 1)], [(3, 2100), (0, 7)]])
-@pytest.mark.parametrize("nq,nkv,d,dv,rot,qt", [(4, 2, 48, 48, 48, None), (6, 2, 24, 16, 8, (0.5, 7)), (4, 4, 16, 32, 16, None),
+@pytest.mark.parametrize("nq,nkv,d,dv,rot,qt", [(6, 2, 48, 48, 48, None), (6, 2, 24, 16, 8, (0.4, 7)), (4, 4, 16, 32, 16, None),
                                                 (3, 1, 40, 40, 0, (0.3, 64)), (2, 2, 18, 10, 6, (0.7, 3)), (2, 1, 20, 20, 12, None)])
 def test_rows_with_a_weighted_norm_per_head_before_an_interleaved_rotation(rts, dtype, entries, nq, nkv, d, dv, rot, qt):
     rt = rts[dtype]
@@ -254,7 +254,7 @@ def test_rows_with_a_weighted_norm_per_head_before_an_interleaved_rotation(rts, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,N,P", [(4, 32, 32), (2, 24, 16), (3, 16, 8), (1, 40, 24), (4, 8, 40), (2, 128, 64)])
+@pytest.mark.parametrize("H,N,P", [(3, 32, 32), (2, 24, 16), (3, 16, 8), (1, 40, 24), (4, 8, 40), (2, 128, 64)])
 def test_constant_decays_over_portions_and_slots(rts, dtype, H, N, P):
     """Three requests in portions of many sizes in one batch (long ones run as chunks of time side by side), one head that
     never forgets: every portion's output equals the plain recurrence over the whole sequence."""
@@ -263,7 +263,7 @@ def test_constant_decays_over_portions_and_slots(rts, dtype, H, N, P):
     lens = [470, 9, 331]
     mk = lambda n, w: torch.randn(n, H * w, generator=g).to(rt.dtype)  # noqa: E731
     qs, ks, vs = ([mk(n, w) for n in lens] for w in (N, N, P))
-    decay = [1.0, 0.6, 0.97, 0.999][:H]
+    decay = [1.0, 0.6, 0.97, 0.995][:H]
     want = []
     for q, k, v in zip(qs, ks, vs):
         qq, kk, vv = (PK.silu(x.double()) for x in (q, k, v))
@@ -301,10 +301,10 @@ def test_small_maps(rts, dtype):
     for F in (24, 257, 1024):
         gu = (3 * torch.randn(T, 2 * F, generator=g)).to(rt.dtype)
         out = torch.full((T, F), float("nan"), dtype=rt.dtype, device=rt.device)
-        rt.ops.clamped_glu(dev(gu), out, 1.5, 1.702, ctx.meta)
-        gg, uu = gu[:, :F].double().clamp(max=1.5), gu[:, F:].double().clamp(-1.5, 1.5)
+        rt.ops.clamped_glu(dev(gu), out, 1.25, 1.702, ctx.meta)
+        gg, uu = gu[:, :F].double().clamp(max=1.25), gu[:, F:].double().clamp(-1.25, 1.25)
         assert torch.allclose(out.float().cpu().double(), gg * torch.sigmoid(1.702 * gg) * (uu + 1), atol=tol * 4)
-    for heads, n, pad in ((4, 48, 64), (3, 10, 16), (8, 128, 128)):
+    for heads, n, pad in ((5, 48, 64), (3, 10, 16), (8, 128, 128)):
         y = torch.randn(T, heads, pad, generator=g).to(rt.dtype)
         gate = torch.randn(T, heads + 5, generator=g).to(rt.dtype)
         yd, gd = dev(y), dev(gate)
@@ -321,7 +321,7 @@ def test_small_maps(rts, dtype):
         want = PK.rms(o.double(), 1e-5) * w.double() * torch.sigmoid(gate[:, 8:].double())
         assert torch.allclose(out.float().cpu().double(), want, atol=tol * 4)
     z = 20 * torch.randn(3, 515, generator=g)
-    for scale, cap in ((2.0, 30.0), (1.0, 0.0), (0.5, 4.0)):
+    for scale, cap in ((2.5, 20.0), (1.0, 0.0), (0.5, 4.0)):
         zd = dev(z.clone())
         rt.ops.scale_softcap(zd, scale, cap, ctx.meta)
         want = cap * torch.tanh(z.double() * scale / cap) if cap else z.double() * scale
@@ -330,7 +330,7 @@ def test_small_maps(rts, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,top,H", [(16, 3, 256), (5, 1, 96), (3, 3, 72), (64, 8, 130)])
+@pytest.mark.parametrize("E,top,H", [(12, 3, 192), (5, 1, 96), (3, 3, 72), (64, 8, 130)])
 def test_router_with_a_bias_and_weights_over_the_chosen(rts, dtype, E, top, H):
     rt = rts[dtype]
     g = torch.Generator().manual_seed(E + H)
