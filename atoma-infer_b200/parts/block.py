@@ -9,15 +9,19 @@ what it leaves IS the residual stream (float32); the sublayers read the stream i
 sequence filter (f1, f2: a short convolution over time, whose state the block keeps per request).  Parameters:
 ``norm``, ``mixer``, ``feed_forward`` (None: the layer has no second sublayer), ``alpha``, ``filter`` (spec or
 None), ``names``.
+
+Parallel and sandwich arrangements: see ``ParallelBlock`` and ``SandwichBlock``.
 """
 from __future__ import annotations
 
-from ..config.registry import part_class, register_part
+from dataclasses import replace
 from typing import Optional
 
 import torch
 
-from .base import Block, apply_pending, join_terms
+from ..config.registry import part_class, register_part
+from ..weights.loader import TensorDecl
+from .base import Block, PendingSum, apply_pending, join_terms
 
 _DEFAULT_NAMES = {"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm",
                   "feed_forward": "mlp"}
@@ -124,7 +128,6 @@ class PostNormBlock(Block):
         apply_pending(ops, resid, delta, ctx)  # a block before this one left its addition pending
         mixer_cache = cache
         if self.mixer.state_bytes() != self.state_bytes() and cache.state is not None:
-            from dataclasses import replace
             mixer_cache = replace(cache, state=self._share(cache.state, "mixer"))
         s1, s2 = self._share(cache.state, "filter1"), self._share(cache.state, "filter2")
         # decode steps: the norm kernel also leaves the next sublayer's input (new row + its short convolution)
@@ -260,7 +263,6 @@ class SandwichBlock(Block):
         return max(p.activation_width() for p in self.parts())
 
     def declare(self):
-        from ..weights.loader import TensorDecl
         pre, n, W = self.prefix, self.names, self.width
         decls = [d for p in self.parts() for d in p.declare()]
         decls += [TensorDecl(pre + n["gate1"], (W, W)), TensorDecl(pre + n["gate1"] + n["gate_bias"], (W,))]
@@ -288,8 +290,6 @@ class SandwichBlock(Block):
         return self._kept_bytes() + self.mixer.state_bytes()
 
     def forward(self, resid, delta, ctx, cache):
-        from dataclasses import replace
-        from .base import PendingSum
         ops, dt, dev, T, W = self.rt.ops, self.rt.dtype, resid.device, ctx.T, self.width
         apply_pending(ops, resid, delta, ctx)  # a block of another kind before this one may have left its addition pending
         kept, mixer_cache = None, cache
